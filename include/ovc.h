@@ -1,0 +1,146 @@
+/*
+ * C ABI of libovc.so: FP8 ExpCast forward attention for NVIDIA B200 (sm_100a).
+ *
+ * The reference project (open-vc-attn 0.3.0) is pure Python and has no FFI of its
+ * own; its device work is reached through Python functions that JIT-compile
+ * Triton and CuTe-DSL kernels.  Each entry point below replaces one of those
+ * device stages and is what a Python/ctypes (or any other FFI) binding of the
+ * path would call.  Citations are paths inside the reference project.
+ *
+ * Conventions
+ *   - Every pointer is a DEVICE pointer unless stated otherwise; the caller owns
+ *     all memory.  No entry point allocates, frees or synchronises, so all of
+ *     them may be captured in a CUDA graph (the one exception is marked).
+ *   - Work is enqueued on `stream` (a cudaStream_t passed as void*) of the
+ *     device that is current in the calling thread.
+ *   - `dtype`: OVC_F16 or OVC_BF16, the element type of the 16-bit inputs.
+ *   - FP8 means E4M3 (float8_e4m3fn), one byte per element.
+ *   - Return value: OVC_OK (0) or a negative OVC_ERR_* code.  Nothing throws.
+ *     ovc_error_string() maps a code to text; ovc_last_cuda_error() returns the
+ *     cudaError_t / CUresult seen by the failing call, if any.
+ *   - Tensors are dense row-major with the shapes given; D is always 128.
+ */
+#ifndef OVC_H
+#define OVC_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define OVC_F16 0
+#define OVC_BF16 1
+
+#define OVC_OK 0
+#define OVC_ERR_ARGUMENT (-1)    /* null pointer, bad size, bad alignment, unknown dtype */
+#define OVC_ERR_CUDA (-2)        /* a CUDA runtime call failed; see ovc_last_cuda_error() */
+#define OVC_ERR_DRIVER (-3)      /* tensor-map creation failed */
+#define OVC_ERR_UNSUPPORTED (-4) /* device is not sm_100 */
+
+/* Bits of the device status word written by ovc_attention (0 = clean run). */
+#define OVC_STATUS_WAIT_EXPIRED 1u /* a bounded barrier wait gave up; the output is invalid */
+
+int ovc_version(void);
+const char* ovc_error_string(int code);
+int ovc_last_cuda_error(void);
+
+/*
+ * Per-(batch, head, 128-token block) FP8 quantisation of Q or K.
+ * Replaces _per_block_quant_kernel / fp8_quantize_per_block_triton
+ * (src/open_vc_attn/quantization.py:153-220).
+ *   x        [B,S,H,128] f16/bf16
+ *   codes    [B,S,H,128] fp8
+ *   descale  [B,H,descale_stride] f32, first ceil(S/128) entries of each row written;
+ *            when descale_stride > ceil(S/128) the entry at ceil(S/128) is set to 1.0
+ *            (the even-count padding of src/open_vc_attn/preparation.py:47-49).
+ */
+int ovc_quantize_per_block(const void* x, int dtype, int64_t B, int64_t S, int64_t H, void* codes,
+                           float* descale, int64_t descale_stride, void* stream);
+
+/*
+ * Per-(batch, head) max |v|.  Replaces the zero fill plus _per_head_amax_kernel
+ * (src/open_vc_attn/quantization.py:22-53,121-134).  amax [B,H] f32 is reset and then reduced into.
+ */
+int ovc_head_amax(const void* v, int dtype, int64_t B, int64_t S, int64_t H, float* amax, void* stream);
+
+/*
+ * V cast with the per-(batch, head) scale 448/max(amax,1e-12); descale = max(amax,1e-12)/448.
+ * Replaces _per_head_scale_cast_kernel and the host division
+ * (src/open_vc_attn/quantization.py:56-93,144).
+ *   codes [B,S,H,128] fp8, descale [B,H] f32.
+ */
+int ovc_quantize_per_head(const void* v, int dtype, int64_t B, int64_t S, int64_t H, const float* amax,
+                          void* codes, float* descale, void* stream);
+
+/*
+ * Fused preparation of one sequence for the packed path.  Replaces prepare_fp8_fused's three
+ * launches _quantize_qk, _per_head_amax_kernel, _cast_pack_v (src/open_vc_attn/preparation.py:83-162).
+ *   q,k,v      [S,H,128] f16/bf16
+ *   q8,k8      [S,H,128] fp8
+ *   v_packed   [H,128,S_pad] fp8, S_pad = ceil(S/128)*128; columns S..S_pad-1 are written as zero
+ *   q_descale  [H,q_blocks] f32, q_blocks = ceil(S/128) rounded up to even (padding entry = 1.0)
+ *   k_descale  [H,ceil(S/128)] f32
+ *   v_descale  [H] f32
+ *   amax_ws    [H] f32 scratch (holds the per-head max |v| afterwards)
+ */
+int ovc_prepare_fused(const void* q, const void* k, const void* v, int dtype, int64_t S, int64_t H,
+                      void* q8, void* k8, void* v_packed, float* q_descale, float* k_descale,
+                      float* v_descale, float* amax_ws, void* stream);
+
+/*
+ * FP8 byte transpose into the packed V layout.  Replaces transpose_v / pack_v
+ * (src/open_vc_attn/_kernels/blackwell/flash_attn/cute/v_layout.py:8-49).
+ *   codes [B,S,H,128] fp8 -> packed [B,H,128,S_pad] fp8 with a zero tail.
+ */
+int ovc_pack_v(const void* codes, int64_t B, int64_t S, int64_t H, void* packed, void* stream);
+
+/*
+ * V cast plus per-token squared rounding residual.  Replaces _v_quant_score_kernel
+ * (src/open_vc_attn/v_repair.py:52-76).
+ *   v [S,H,128] f16/bf16, amax [H] f32 -> codes [S,H,128] fp8, score [H,S] f32.
+ */
+int ovc_repair_score(const void* v, int dtype, int64_t S, int64_t H, const float* amax, void* codes,
+                     float* score, void* stream);
+
+/*
+ * Builds the repair prefix.  Replaces _repair_rows_kernel (src/open_vc_attn/v_repair.py:79-113).
+ *   k_all,v_all [rows+S,H,128] fp8: rows [rows, rows+S) hold the original codes on entry; rows
+ *               [0, rows) are written (key copies; V residual codes, zero for pad rows >= selected)
+ *   v_src       [S,H,128] f16/bf16 original V
+ *   k_descale   [H,k_blocks] f32, v_descale [H] f32
+ *   index       [H,selected] int32 source token of each repair row
+ *   repair_kd   [H,rows] f32 out: the source token's K descale
+ */
+int ovc_repair_rows(void* k_all, void* v_all, const void* v_src, int dtype, const float* k_descale,
+                    const float* v_descale, const int32_t* index, float* repair_kd, int64_t selected,
+                    int64_t rows, int64_t S, int64_t H, int64_t k_blocks, void* stream);
+
+/*
+ * FP8 ExpCast forward attention.  Replaces the compiled FlashAttentionForwardSm100 kernel behind
+ * _flash_attn_fwd (src/open_vc_attn/_kernels/blackwell/flash_attn/cute/interface.py:110-179,
+ * cute/flash_fwd_sm100.py:1438) for non-causal MHA, D = 128, with per-block Q/K and per-head V descales.
+ *   q8          [B,Sq,H,128] fp8
+ *   k8          [B,Sk,H,128] fp8 (Sk includes the repair prefix when repair_rows > 0)
+ *   v_packed    [B,H,128,Sk_pad] fp8, Sk_pad = ceil(Sk/128)*128
+ *   q_descale   [B,H,q_blocks] f32 with q_blocks >= ceil(Sq/128)
+ *   k_descale   [B,H,ceil(Sk/128)] f32
+ *   v_descale   [B,H] f32
+ *   repair_kd   [H,repair_rows] f32 or NULL; repair_rows is a multiple of 128, < Sk, and needs B == 1
+ *   out         [B,Sq,H,128] bf16
+ *   softmax_scale   > 0 and finite
+ *   mid_window_blocks  >= 0: start the key scan that many 128-key blocks right of the diagonal;
+ *                      -1: plain right-to-left scan
+ *   status      one uint32 in device memory, OR-ed with OVC_STATUS_* bits by the kernel; the caller
+ *               clears it and reads it back when it wants to check.  May be NULL.
+ * Creates its tensor maps on the host with the driver's cuTensorMapEncodeTiled; no device allocation.
+ */
+int ovc_attention(const void* q8, const void* k8, const void* v_packed, const float* q_descale,
+                  int64_t q_blocks, const float* k_descale, const float* v_descale, const float* repair_kd,
+                  int64_t repair_rows, void* out, int64_t B, int64_t Sq, int64_t Sk, int64_t H,
+                  float softmax_scale, int mid_window_blocks, uint32_t* status, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* OVC_H */

@@ -1,0 +1,565 @@
+// FP8 ExpCast forward attention for sm_100a: TMA -> shared memory -> tcgen05 FP8 MMA with
+// accumulators in tensor memory, score -> FP8 probability conversion on CUDA cores.
+//
+// One CTA owns 256 query rows of one (batch, head): two 128-row stages that ping-pong through one
+// score buffer in tensor memory.  Warp roles: warps 0-3 convert scores of stage 0, warps 4-7 of
+// stage 1, warp 8 issues TMA loads, warp 9 issues MMAs; warps 10-11 only take part in register
+// reallocation.  Numerics follow the reference's packed kernel
+// (src/open_vc_attn/_kernels/blackwell/flash_attn/cute/flash_fwd_sm100.py:3513-3911 with
+// cute/softmax.py:203-248 and cute/utils.py:704-795): running max in the descaled domain,
+// ExpCast codes from one FMA and an FP16-subnormal rounding, denominator summed by the tensor core
+// through a block of ones appended to the V tile.
+//
+// Tensor memory map (512 columns): S 0..127 (shared by both stages), P0 128..159, P1 160..191,
+// O0 192..335, O1 336..479; each O region is 128 output columns followed by 16 copies of the
+// denominator (the PV product has N = 144).
+
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <math.h>
+
+#include "common.cuh"
+#include "sm100_ptx.cuh"
+
+namespace ovc {
+namespace {
+
+using namespace ptx;
+
+constexpr int kThreads = 384;
+constexpr int kKStages = 3;
+constexpr int kVStages = 3;
+constexpr int kTileBytes = kTile * kDim;          // 16384: one FP8 tile, 128 rows of 128 bytes
+constexpr int kOnesRows = 16;                     // extension of the PV product that sums P
+constexpr int kVSlotBytes = kTileBytes + kOnesRows * 128;
+constexpr int kPvN = kDim + kOnesRows;            // 144
+constexpr uint32_t kColS = 0, kColP = 128, kColO = 192, kColOStride = 144, kTmemCols = 512;
+constexpr long long kWaitCycles = 400000000LL;    // bounded barrier wait (~0.2 s)
+
+struct SmemLayout {
+    alignas(1024) uint8_t q[2][kTileBytes];
+    alignas(1024) uint8_t k[kKStages][kTileBytes];
+    alignas(1024) uint8_t v[kVStages][kVSlotBytes];
+    alignas(8) uint64_t q_full[2];
+    uint64_t k_full[kKStages], k_empty[kKStages];
+    uint64_t v_full[kVStages], v_empty[kVStages];
+    uint64_t s_full[2], s_empty, p_full[2], o_full[2], drain;
+    uint32_t tmem_base;
+    volatile uint32_t abort_flag;
+};
+
+struct AttnParams {
+    const float* q_descale;  // [B,H,q_blocks]
+    const float* k_descale;  // [B,H,n_tiles]
+    const float* v_descale;  // [B,H]
+    const float* repair_kd;  // [H,repair_rows] or null
+    __nv_bfloat16* out;      // [B,Sq,H,128]
+    uint32_t* status;
+    long long Sq, Sk;
+    int H, B, q_blocks, n_tiles, first_tile, m_blocks, mid_window;
+    float scale_log2;
+};
+
+// Key tile visited at step `it`: from j0 down to first_tile, then from the right edge down to
+// j0 + 1, then the repair prefix from first_tile - 1 down to 0.
+__device__ __forceinline__ int tile_at(int it, int j0, int first_tile, int n_tiles) {
+    const int len1 = j0 - first_tile + 1;
+    const int originals = n_tiles - first_tile;
+    if (it < len1) return j0 - it;
+    if (it < originals) return n_tiles - 1 - (it - len1);
+    return first_tile - 1 - (it - originals);
+}
+
+// Bounded wait.  Returns false when the barrier did not complete in time or another thread of
+// the CTA already gave up; the caller then leaves its loop and the CTA tears down.
+__device__ __forceinline__ bool wait_bar(SmemLayout& sm, uint64_t* bar, uint32_t parity, uint32_t* status) {
+    const uint32_t addr = smem_addr(bar);
+    if (mbar_try_wait(addr, parity)) return true;
+    const long long start = clock64();
+    while (true) {
+        if (mbar_try_wait(addr, parity)) return true;
+        if (sm.abort_flag) return false;
+        if (clock64() - start > kWaitCycles) {
+            sm.abort_flag = 1;
+            if (status != nullptr) atomicOr(status, OVC_STATUS_WAIT_EXPIRED);
+            return false;
+        }
+    }
+}
+
+#ifdef OVC_DEBUG_DUMP
+// Debug builds only: raw scores and codes of CTA 0's first key tile go to this buffer.
+__device__ float* g_debug_dump = nullptr;
+#endif
+
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
+
+__device__ __forceinline__ float ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+// bias = RD(-row_max * code_scale + 119.65 * 2^-24)
+__device__ __forceinline__ float expcast_bias(float row_max, float code_scale) {
+    float b;
+    asm("fma.rm.f32 %0, %1, %2, 0f36EF4CCD;" : "=f"(b) : "f"(-row_max), "f"(code_scale));
+    return b;
+}
+
+__device__ __forceinline__ uint64_t pack2(float a, float b) {
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(a), "f"(b));
+    return r;
+}
+
+// Four scores -> four ExpCast E4M3 codes: y = x*scale + bias (units of 2^-24), rounded to an FP16
+// subnormal whose low byte is the integer code; ReLU supplies the clamp at zero.
+__device__ __forceinline__ uint32_t encode4(uint32_t x0, uint32_t x1, uint32_t x2, uint32_t x3, uint64_t scale2,
+                                            uint64_t bias2) {
+    uint32_t out;
+    asm("{\n\t.reg .b64 xp, r;\n\t.reg .f32 f0, f1, f2, f3;\n\t.reg .b32 lo, hi;\n\t"
+        "mov.b64 xp, {%1, %2};\n\tfma.rn.f32x2 r, xp, %5, %6;\n\tmov.b64 {f0, f1}, r;\n\t"
+        "mov.b64 xp, {%3, %4};\n\tfma.rn.f32x2 r, xp, %5, %6;\n\tmov.b64 {f2, f3}, r;\n\t"
+        "cvt.rn.relu.f16x2.f32 lo, f1, f0;\n\tcvt.rn.relu.f16x2.f32 hi, f3, f2;\n\t"
+        "prmt.b32 %0, lo, hi, 0x6420;\n\t}"
+        : "=r"(out)
+        : "r"(x0), "r"(x1), "r"(x2), "r"(x3), "l"(scale2), "l"(bias2));
+    return out;
+}
+
+__device__ __forceinline__ uint32_t bf16x2(float lo, float hi) {
+    uint32_t r;
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+    return r;
+}
+
+__global__ void __launch_bounds__(kThreads, 1)
+attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
+                 const __grid_constant__ CUtensorMap tmap_v, const AttnParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    SmemLayout& sm = *reinterpret_cast<SmemLayout*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+
+    // A barrier wait already expired in this launch: do not start more work.  One thread reads the
+    // word so that the whole CTA takes the same decision.
+    __shared__ uint32_t skip_cta;
+    if (threadIdx.x == 0) skip_cta = p.status != nullptr ? *reinterpret_cast<volatile uint32_t*>(p.status) : 0u;
+    __syncthreads();
+    if (skip_cta != 0) return;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int m_block = blockIdx.x % p.m_blocks;
+    const int bh = blockIdx.x / p.m_blocks;
+    const int head = bh % p.H, batch = bh / p.H;
+    const int n_iters = p.n_tiles;
+    const int j0 = p.mid_window < 0 ? p.n_tiles - 1
+                                    : min(2 * m_block + p.first_tile + p.mid_window, p.n_tiles - 1);
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(smem_addr(&sm.q_full[i]), 1);
+            mbar_init(smem_addr(&sm.s_full[i]), 1);
+            mbar_init(smem_addr(&sm.p_full[i]), 128);
+            mbar_init(smem_addr(&sm.o_full[i]), 1);
+        }
+        for (int i = 0; i < kKStages; ++i) {
+            mbar_init(smem_addr(&sm.k_full[i]), 1);
+            mbar_init(smem_addr(&sm.k_empty[i]), 1);
+        }
+        for (int i = 0; i < kVStages; ++i) {
+            mbar_init(smem_addr(&sm.v_full[i]), 1);
+            mbar_init(smem_addr(&sm.v_empty[i]), 1);
+        }
+        mbar_init(smem_addr(&sm.s_empty), 128);
+        mbar_init(smem_addr(&sm.drain), 1);
+        sm.abort_flag = 0;
+        mbar_init_fence();
+    }
+    // Rows 128..143 of every V slot: E4M3 1.0, so PV also accumulates the row sums of P.
+    for (int i = threadIdx.x; i < kVStages * kOnesRows * 128 / 4; i += kThreads) {
+        const int slot = i / (kOnesRows * 128 / 4), w = i % (kOnesRows * 128 / 4);
+        reinterpret_cast<uint32_t*>(&sm.v[slot][kTileBytes])[w] = 0x38383838u;
+    }
+    fence_proxy_async_smem();
+    if (warp == 9) {
+        tmem_alloc(smem_addr(&sm.tmem_base), kTmemCols);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = sm.tmem_base;
+
+    if (warp >= 8) {
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
+        if (warp == 8) {
+            // ---------------- TMA producer ----------------
+            if (lane == 0) {
+                tma_prefetch_desc(&tmap_q);
+                tma_prefetch_desc(&tmap_k);
+                tma_prefetch_desc(&tmap_v);
+                const uint64_t keep = policy_evict_last(), stream = policy_evict_first();
+                for (int s = 0; s < 2; ++s) {
+                    mbar_expect_tx(smem_addr(&sm.q_full[s]), kTileBytes);
+                    tma_load_4d(smem_addr(sm.q[s]), &tmap_q, smem_addr(&sm.q_full[s]), 0, head,
+                                (2 * m_block + s) * kTile, batch, stream);
+                }
+                int it = 0;
+                for (; it < n_iters; ++it) {
+                    const int j = tile_at(it, j0, p.first_tile, p.n_tiles);
+                    const int ks = it % kKStages, vs = it % kVStages;
+                    if (!wait_bar(sm, &sm.k_empty[ks], ((it / kKStages) & 1) ^ 1, p.status)) break;
+                    mbar_expect_tx(smem_addr(&sm.k_full[ks]), kTileBytes);
+                    tma_load_4d(smem_addr(sm.k[ks]), &tmap_k, smem_addr(&sm.k_full[ks]), 0, head, j * kTile, batch, keep);
+                    if (!wait_bar(sm, &sm.v_empty[vs], ((it / kVStages) & 1) ^ 1, p.status)) break;
+                    mbar_expect_tx(smem_addr(&sm.v_full[vs]), kTileBytes);
+                    tma_load_4d(smem_addr(sm.v[vs]), &tmap_v, smem_addr(&sm.v_full[vs]), j * kTile, 0, head, batch, keep);
+                }
+                if (sm.abort_flag) {
+                    // Give the copies already issued a bounded time to land before the CTA exits.
+                    const int issued_k = min(it + 1, n_iters), issued_v = it;
+                    for (int s = 0; s < kKStages; ++s) {
+                        const int last = issued_k - 1 - ((issued_k - 1 - s) % kKStages + kKStages) % kKStages;
+                        if (issued_k > 0 && last >= 0) {
+                            const long long t0 = clock64();
+                            while (!mbar_try_wait(smem_addr(&sm.k_full[s]), (last / kKStages) & 1) &&
+                                   clock64() - t0 < kWaitCycles) {}
+                        }
+                    }
+                    for (int s = 0; s < kVStages; ++s) {
+                        const int last = issued_v - 1 - ((issued_v - 1 - s) % kVStages + kVStages) % kVStages;
+                        if (issued_v > 0 && last >= 0) {
+                            const long long t0 = clock64();
+                            while (!mbar_try_wait(smem_addr(&sm.v_full[s]), (last / kVStages) & 1) &&
+                                   clock64() - t0 < kWaitCycles) {}
+                        }
+                    }
+                    const long long t0 = clock64();
+                    while (!(mbar_try_wait(smem_addr(&sm.q_full[0]), 0) && mbar_try_wait(smem_addr(&sm.q_full[1]), 0)) &&
+                           clock64() - t0 < kWaitCycles) {}
+                }
+            }
+        } else if (warp == 9) {
+            // ---------------- MMA issuer ----------------
+            constexpr uint32_t idesc_qk = idesc_e4m3_f32(kTile);
+            constexpr uint32_t idesc_pv = idesc_e4m3_f32(kPvN);
+            bool ok = wait_bar(sm, &sm.q_full[0], 0, p.status) && wait_bar(sm, &sm.q_full[1], 0, p.status);
+            ok = __all_sync(0xFFFFFFFFu, ok);
+            for (int it = 0; ok && it <= n_iters; ++it) {
+                const int ks = it % kKStages;
+                if (it < n_iters) ok = wait_bar(sm, &sm.k_full[ks], (it / kKStages) & 1, p.status);
+                const int pv = it - 1, vs = (pv + kVStages) % kVStages;
+                if (ok && it > 0) ok = wait_bar(sm, &sm.v_full[vs], (pv / kVStages) & 1, p.status);
+                ok = __all_sync(0xFFFFFFFFu, ok);
+                for (int s = 0; ok && s < 2; ++s) {
+                    if (it > 0) {
+                        // O[s] (+)= P[s] * [V | 1]
+                        ok = __all_sync(0xFFFFFFFFu, wait_bar(sm, &sm.p_full[s], pv & 1, p.status));
+                        if (!ok) break;
+                        tc_fence_after();
+                        if (lane == 0) {
+                            const uint64_t b = smem_desc_sw128(smem_addr(sm.v[vs]));
+                            const uint32_t d = tmem + kColO + s * kColOStride, a = tmem + kColP + 32 * s;
+#pragma unroll
+                            for (int kk = 0; kk < 4; ++kk)
+                                mma_f8_ts(d, a + 8 * kk, b + 2 * kk, idesc_pv, (pv > 0 || kk > 0) ? 1u : 0u);
+                            if (s == 1) mma_commit(smem_addr(&sm.v_empty[vs]));
+                            if (it == n_iters) mma_commit(smem_addr(&sm.o_full[s]));
+                        }
+                        __syncwarp();
+                    }
+                    if (it < n_iters) {
+                        // S = Q[s] * K^T once the previous scores have left tensor memory
+                        if (it > 0 || s > 0) {
+                            ok = __all_sync(0xFFFFFFFFu, wait_bar(sm, &sm.s_empty, (2 * it + s - 1) & 1, p.status));
+                            if (!ok) break;
+                            tc_fence_after();
+                        }
+                        if (lane == 0) {
+                            const uint64_t a = smem_desc_sw128(smem_addr(sm.q[s]));
+                            const uint64_t b = smem_desc_sw128(smem_addr(sm.k[ks]));
+#pragma unroll
+                            for (int kk = 0; kk < 4; ++kk)
+                                mma_f8_ss(tmem + kColS, a + 2 * kk, b + 2 * kk, idesc_qk, kk > 0 ? 1u : 0u);
+                            mma_commit(smem_addr(&sm.s_full[s]));
+                            if (s == 1) mma_commit(smem_addr(&sm.k_empty[ks]));
+                        }
+                        __syncwarp();
+                    }
+                }
+            }
+            if (!ok) {
+                // Let MMAs already issued finish before tensor memory is released.
+                if (lane == 0) mma_commit(smem_addr(&sm.drain));
+                __syncwarp();
+                const long long t0 = clock64();
+                while (!mbar_try_wait(smem_addr(&sm.drain), 0) && clock64() - t0 < kWaitCycles) {}
+            }
+        }
+    } else {
+        // ---------------- score conversion: one query row per thread ----------------
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 232;");
+        const int stage = warp >> 2;
+        const int row_in_tile = (warp & 3) * 32 + lane;
+        const uint32_t lane_base = tmem + (static_cast<uint32_t>((warp & 3) * 32) << 16);
+        const uint32_t t_s = lane_base + kColS, t_p = lane_base + kColP + 32 * stage;
+        const uint32_t t_o = lane_base + kColO + stage * kColOStride;
+        const int q_tile = 2 * m_block + stage;
+        const long long bh_l = static_cast<long long>(batch) * p.H + head;
+        const float qd = q_tile < p.q_blocks ? __ldg(p.q_descale + bh_l * p.q_blocks + q_tile) : 1.0f;
+        const float sigma = p.scale_log2 * qd;
+        const float code_scale0 = sigma * 4.76837158203125e-07f;  // sigma * 8 * 2^-24
+        const float* kd_row = p.k_descale + bh_l * p.n_tiles;
+        const int tail_valid = static_cast<int>(p.Sk - static_cast<long long>(p.n_tiles - 1) * kTile);
+
+        float row_max = 0.0f, saved_denominator = 0.0f;
+        bool ok = true;
+        for (int it = 0; it < n_iters; ++it) {
+            const int j = tile_at(it, j0, p.first_tile, p.n_tiles);
+            const float kd = __ldg(kd_row + j);
+            ok = __all_sync(0xFFFFFFFFu, wait_bar(sm, &sm.s_full[stage], it & 1, p.status));
+            if (!ok) break;
+            tc_fence_after();
+            uint32_t s[128];
+            tmem_ld32(t_s, s);
+            tmem_ld32(t_s + 32, s + 32);
+            tmem_ld32(t_s + 64, s + 64);
+            tmem_ld32(t_s + 96, s + 96);
+            tmem_wait_ld();
+            tc_fence_before();
+            mbar_arrive(smem_addr(&sm.s_empty));
+
+#ifdef OVC_DEBUG_DUMP
+            if (g_debug_dump != nullptr && blockIdx.x == 0 && it == 0) {
+                float* d = g_debug_dump + (stage * 128 + row_in_tile) * 128;
+                for (int c = 0; c < 128; ++c) d[c] = __uint_as_float(s[c]);
+            }
+#endif
+            if (j == p.n_tiles - 1 && tail_valid < kTile) {
+#pragma unroll
+                for (int c = 0; c < 128; ++c)
+                    if (c >= tail_valid) s[c] = 0xFF800000u;  // -inf
+            }
+            if (j < p.first_tile) {
+                // Repair keys come from different K blocks: each column carries its own K descale.
+                const float4* kd4 = reinterpret_cast<const float4*>(p.repair_kd + static_cast<long long>(head) * p.first_tile * kTile + j * kTile);
+#pragma unroll
+                for (int c = 0; c < 32; ++c) {
+                    const float4 f = __ldg(kd4 + c);
+                    s[4 * c] = __float_as_uint(__uint_as_float(s[4 * c]) * f.x);
+                    s[4 * c + 1] = __float_as_uint(__uint_as_float(s[4 * c + 1]) * f.y);
+                    s[4 * c + 2] = __float_as_uint(__uint_as_float(s[4 * c + 2]) * f.z);
+                    s[4 * c + 3] = __float_as_uint(__uint_as_float(s[4 * c + 3]) * f.w);
+                }
+            }
+            // Row max of the tile, three inputs per instruction.
+            float m9[43];
+#pragma unroll
+            for (int c = 0; c < 42; ++c)
+                m9[c] = fmax3(__uint_as_float(s[3 * c]), __uint_as_float(s[3 * c + 1]), __uint_as_float(s[3 * c + 2]));
+            m9[42] = fmaxf(__uint_as_float(s[126]), __uint_as_float(s[127]));
+            float m3[15];
+#pragma unroll
+            for (int c = 0; c < 14; ++c) m3[c] = fmax3(m9[3 * c], m9[3 * c + 1], m9[3 * c + 2]);
+            m3[14] = m9[42];
+            float m1[5];
+#pragma unroll
+            for (int c = 0; c < 5; ++c) m1[c] = fmax3(m3[3 * c], m3[3 * c + 1], m3[3 * c + 2]);
+            const float tile_max = fmaxf(fmax3(m1[0], m1[1], m1[2]), fmaxf(m1[3], m1[4])) * kd;
+
+            float alpha = 0.0f;
+            float new_max = tile_max;
+            if (it > 0) {
+                new_max = fmaxf(row_max, tile_max);
+                const float safe = new_max == -INFINITY ? 0.0f : new_max;
+                alpha = ex2((row_max - safe) * sigma);
+            }
+            row_max = new_max;
+            const float safe_max = new_max == -INFINITY ? 0.0f : new_max;
+            const float bias = expcast_bias(safe_max, code_scale0);
+            const float code_scale = code_scale0 * kd;
+            const uint64_t scale2 = pack2(code_scale, code_scale), bias2 = pack2(bias, bias);
+            uint32_t codes[32];
+#pragma unroll
+            for (int c = 0; c < 32; ++c) codes[c] = encode4(s[4 * c], s[4 * c + 1], s[4 * c + 2], s[4 * c + 3], scale2, bias2);
+            tmem_st32(t_p, codes);
+#ifdef OVC_DEBUG_DUMP
+            if (g_debug_dump != nullptr && blockIdx.x == 0 && it == 0) {
+                uint32_t* d = reinterpret_cast<uint32_t*>(g_debug_dump) + 256 * 128 + (stage * 128 + row_in_tile) * 32;
+                for (int c = 0; c < 32; ++c) d[c] = codes[c];
+            }
+#endif
+
+            if (p.first_tile > 0 && j == p.first_tile - 1) {
+                // First repair tile: the denominator holds the original tokens' total only.
+                saved_denominator = __uint_as_float(tmem_ld1(t_o + kDim));
+                tmem_wait_ld();
+            }
+            if (it > 0 && __any_sync(0xFFFFFFFFu, alpha < 1.0f)) {
+                // The running max moved: rescale the accumulator and the denominator in place.
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    uint32_t o[32];
+                    tmem_ld32(t_o + 32 * c, o);
+                    tmem_wait_ld();
+#pragma unroll
+                    for (int e = 0; e < 32; ++e) o[e] = __float_as_uint(__uint_as_float(o[e]) * alpha);
+                    tmem_st32(t_o + 32 * c, o);
+                }
+                const float l = __uint_as_float(tmem_ld1(t_o + kDim));
+                tmem_wait_ld();
+                tmem_st1(t_o + kDim, __float_as_uint(l * alpha));
+            }
+            tmem_wait_st();
+            tc_fence_before();
+            mbar_arrive(smem_addr(&sm.p_full[stage]));
+        }
+        if (ok) ok = __all_sync(0xFFFFFFFFu, wait_bar(sm, &sm.o_full[stage], 0, p.status));
+        if (ok) {
+            tc_fence_after();
+            float l = __uint_as_float(tmem_ld1(t_o + kDim));
+            tmem_wait_ld();
+            if (p.first_tile > 0) l = saved_denominator;
+            const bool bad = l == 0.0f || l != l;
+            float inv;
+            asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(inv) : "f"(bad ? 1.0f : l));
+            const float factor = inv * __ldg(p.v_descale + bh_l);
+            const long long row = static_cast<long long>(q_tile) * kTile + row_in_tile;
+            uint4* dst = reinterpret_cast<uint4*>(p.out + ((static_cast<long long>(batch) * p.Sq + row) * p.H + head) * kDim);
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                uint32_t o[32];
+                tmem_ld32(t_o + 32 * c, o);
+                tmem_wait_ld();
+                if (row < p.Sq) {
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        uint4 w;
+                        w.x = bf16x2(__uint_as_float(o[8 * e]) * factor, __uint_as_float(o[8 * e + 1]) * factor);
+                        w.y = bf16x2(__uint_as_float(o[8 * e + 2]) * factor, __uint_as_float(o[8 * e + 3]) * factor);
+                        w.z = bf16x2(__uint_as_float(o[8 * e + 4]) * factor, __uint_as_float(o[8 * e + 5]) * factor);
+                        w.w = bf16x2(__uint_as_float(o[8 * e + 6]) * factor, __uint_as_float(o[8 * e + 7]) * factor);
+                        dst[4 * c + e] = w;
+                    }
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 9) {
+        tc_fence_after();
+        tmem_dealloc(tmem, kTmemCols);
+    }
+}
+
+// ---- host side -------------------------------------------------------------------------------
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled_fn() {
+    static EncodeTiledFn fn = []() -> EncodeTiledFn {
+        void* ptr = nullptr;
+        cudaDriverEntryPointQueryResult result;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &result) != cudaSuccess ||
+            result != cudaDriverEntryPointSuccess)
+            return nullptr;
+        return reinterpret_cast<EncodeTiledFn>(ptr);
+    }();
+    return fn;
+}
+
+// 4-D byte tensor (innermost first) with a 128-byte-swizzled box of box0 x box1 x 1 x 1.
+int make_map(CUtensorMap* map, const void* base, const cuuint64_t (&dims)[4], const cuuint64_t (&strides)[3],
+             cuuint32_t box0, cuuint32_t box1_dim, int box1_axis) {
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (fn == nullptr) return OVC_ERR_DRIVER;
+    cuuint32_t box[4] = {box0, 1, 1, 1};
+    box[box1_axis] = box1_dim;
+    const cuuint32_t elem[4] = {1, 1, 1, 1};
+    const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, const_cast<void*>(base), dims, strides, box, elem,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        set_last_cuda_error(static_cast<int>(r));
+        return OVC_ERR_DRIVER;
+    }
+    return OVC_OK;
+}
+
+}  // namespace
+}  // namespace ovc
+
+using namespace ovc;
+
+#ifdef OVC_DEBUG_DUMP
+extern "C" int ovc_debug_set_dump(float* buffer) {
+    return cudaMemcpyToSymbol(g_debug_dump, &buffer, sizeof(buffer)) == cudaSuccess ? 0 : -2;
+}
+#endif
+
+extern "C" int ovc_attention(const void* q8, const void* k8, const void* v_packed, const float* q_descale,
+                             int64_t q_blocks, const float* k_descale, const float* v_descale, const float* repair_kd,
+                             int64_t repair_rows, void* out, int64_t B, int64_t Sq, int64_t Sk, int64_t H,
+                             float softmax_scale, int mid_window_blocks, uint32_t* status, void* stream) {
+    if (!q8 || !k8 || !v_packed || !q_descale || !k_descale || !v_descale || !out || B < 1 || Sq < 1 || Sk < 1 ||
+        H < 1 || Sq > (1LL << 30) || Sk > (1LL << 30) || q_blocks < ceil_div(Sq, kTile) || !(softmax_scale > 0.0f) ||
+        !isfinite(softmax_scale) || mid_window_blocks < -1 || repair_rows < 0 || repair_rows % kTile != 0 ||
+        (repair_rows > 0 && (repair_kd == nullptr || repair_rows >= Sk || B != 1)) || !aligned16(q8) ||
+        !aligned16(k8) || !aligned16(v_packed) || !aligned16(out) || (repair_kd && !aligned16(repair_kd)))
+        return OVC_ERR_ARGUMENT;
+    const int64_t n_tiles = ceil_div(Sk, kTile), Sk_pad = n_tiles * kTile;
+    const int64_t m_blocks = ceil_div(Sq, 2 * kTile);
+    if (m_blocks * H * B > 0x7FFFFFFFLL) return OVC_ERR_ARGUMENT;
+
+    int device = 0;
+    cudaError_t err = cudaGetDevice(&device);
+    int major = 0;
+    if (err == cudaSuccess) err = cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, device);
+    if (err != cudaSuccess) { set_last_cuda_error(err); return OVC_ERR_CUDA; }
+    if (major != 10) return OVC_ERR_UNSUPPORTED;
+
+    CUtensorMap map_q, map_k, map_v;
+    {
+        const cuuint64_t dq[4] = {128, static_cast<cuuint64_t>(H), static_cast<cuuint64_t>(Sq), static_cast<cuuint64_t>(B)};
+        const cuuint64_t sq[3] = {128, static_cast<cuuint64_t>(H) * 128, static_cast<cuuint64_t>(Sq) * H * 128};
+        int rc = make_map(&map_q, q8, dq, sq, 128, 128, 2);
+        if (rc != OVC_OK) return rc;
+        const cuuint64_t dk[4] = {128, static_cast<cuuint64_t>(H), static_cast<cuuint64_t>(Sk), static_cast<cuuint64_t>(B)};
+        const cuuint64_t sk[3] = {128, static_cast<cuuint64_t>(H) * 128, static_cast<cuuint64_t>(Sk) * H * 128};
+        rc = make_map(&map_k, k8, dk, sk, 128, 128, 2);
+        if (rc != OVC_OK) return rc;
+        // Extent Sk (not Sk_pad) along the keys: the padded tail reads as zero whatever it holds.
+        const cuuint64_t dv[4] = {static_cast<cuuint64_t>(Sk), 128, static_cast<cuuint64_t>(H), static_cast<cuuint64_t>(B)};
+        const cuuint64_t sv[3] = {static_cast<cuuint64_t>(Sk_pad), static_cast<cuuint64_t>(Sk_pad) * 128,
+                                  static_cast<cuuint64_t>(Sk_pad) * 128 * H};
+        rc = make_map(&map_v, v_packed, dv, sv, 128, 128, 1);
+        if (rc != OVC_OK) return rc;
+    }
+
+    AttnParams p{};
+    p.q_descale = q_descale, p.k_descale = k_descale, p.v_descale = v_descale, p.repair_kd = repair_kd;
+    p.out = static_cast<__nv_bfloat16*>(out), p.status = status;
+    p.Sq = Sq, p.Sk = Sk, p.H = static_cast<int>(H), p.B = static_cast<int>(B);
+    p.q_blocks = static_cast<int>(q_blocks), p.n_tiles = static_cast<int>(n_tiles);
+    p.first_tile = static_cast<int>(repair_rows / kTile), p.m_blocks = static_cast<int>(m_blocks);
+    p.mid_window = mid_window_blocks;
+    p.scale_log2 = static_cast<float>(static_cast<double>(softmax_scale) * 1.4426950408889634);
+
+    const size_t smem_bytes = sizeof(SmemLayout) + 1024;
+    static bool configured[64] = {};
+    if (device < 64 && !configured[device]) {
+        err = cudaFuncSetAttribute(attention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem_bytes));
+        if (err != cudaSuccess) { set_last_cuda_error(err); return OVC_ERR_CUDA; }
+        configured[device] = true;
+    }
+    const unsigned grid = static_cast<unsigned>(m_blocks * H * B);
+    attention_kernel<<<grid, kThreads, smem_bytes, static_cast<cudaStream_t>(stream)>>>(map_q, map_k, map_v, p);
+    return check_launch();
+}

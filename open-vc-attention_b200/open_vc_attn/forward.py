@@ -1,0 +1,173 @@
+"""Host interface of the attention kernel (ovc_attention in libovc.so).
+
+Takes the argument contract that the reference's public functions hand to its kernel interface
+``_flash_attn_fwd(q, k, v, **kwargs) -> (out, lse)``
+(src/open_vc_attn/_kernels/blackwell/flash_attn/cute/interface.py:110-179), restricted to what
+those functions use: FP8 E4M3 Q/K/V with FP32 descales, ExpCast, non-causal, no LSE, optional
+prepacked V and optional repair prefix.  Anything else raises instead of degrading.
+"""
+
+import math
+
+import torch
+
+from . import _lib
+
+_status_words = {}
+
+
+def status_word(device):
+    """One sticky uint32 per device that the kernel ORs error bits into."""
+    key = torch.device(device).index
+    if key not in _status_words:
+        _status_words[key] = torch.zeros(1, dtype=torch.int32, device=device)
+    return _status_words[key]
+
+
+def check_status(device):
+    """Synchronise and raise if any attention launch on ``device`` gave up on a barrier wait."""
+    word = status_word(device)
+    value = int(word.item())
+    if value != 0:
+        word.zero_()
+        raise RuntimeError(f"open_vc_attn attention kernel reported status {value:#x} (bounded wait expired)")
+
+
+def _validate_packed_view(v):
+    # src/open_vc_attn/_kernels/blackwell/flash_attn/cute/interface.py:206-217
+    if v.ndim != 3:
+        raise ValueError("v_prepacked requires a single-sequence [S,H,128] view")
+    length, heads, dim = v.shape
+    padded = (length + 127) // 128 * 128
+    if (
+        dim != 128
+        or v.dtype != torch.float8_e4m3fn
+        or tuple(v.stride()) != (1, dim * padded, padded)
+        or v.storage_offset() != 0
+        or v.untyped_storage().nbytes() < heads * dim * padded
+    ):
+        raise ValueError("v_prepacked must use the padded sequence-contiguous FP8 layout")
+
+
+def flash_attn_fwd(
+    q,
+    k,
+    v,
+    *,
+    q_descale=None,
+    k_descale=None,
+    v_descale=None,
+    cu_seqlens_q=None,
+    cu_seqlens_k=None,
+    max_seqlen_q=None,
+    max_seqlen_k=None,
+    expcast=False,
+    v_prepacked=False,
+    causal=False,
+    softmax_scale=None,
+    mid_window_blocks=None,
+    return_lse=False,
+    repair_k_descale=None,
+    **unsupported,
+):
+    """FP8 ExpCast attention.  Returns (out bf16 in Q's shape, None).
+
+    q [Sq,H,128] or [B,Sq,H,128] e4m3; k the same with Sk; v like k, or (v_prepacked) the logical
+    [Sk,H,128] view of a [H,128,Sk_pad] buffer.  q_descale [B,H,>=ceil(Sq/128)], k_descale
+    [B,H,ceil(Sk/128)], v_descale [B,H], all float32.  cu_seqlens_* / max_seqlen_* are accepted for
+    signature compatibility; a 3-D call is one sequence spanning the whole tensor.
+    """
+    if unsupported:
+        raise NotImplementedError(f"Unsupported kernel options in this build: {sorted(unsupported)}")
+    if not expcast:
+        raise NotImplementedError("Only the ExpCast FP8 path (expcast=True) is built")
+    if causal:
+        raise NotImplementedError("causal=True is not built; this engine is dense non-causal attention")
+    if return_lse:
+        raise NotImplementedError("return_lse=True is not built")
+    if any(t.dtype != torch.float8_e4m3fn for t in (q, k, v)):
+        raise ValueError("ExpCast attention expects float8_e4m3fn Q/K/V")
+    if q_descale is None or k_descale is None or v_descale is None:
+        raise ValueError("ExpCast attention expects q_descale, k_descale and v_descale")
+    if v_prepacked:
+        _validate_packed_view(v)
+    if q.ndim not in (3, 4) or k.ndim != q.ndim or q.shape[-1] != 128 or k.shape[-1] != 128:
+        raise ValueError("Expected [S,H,128] or [B,S,H,128] Q/K")
+    if softmax_scale is None:
+        softmax_scale = 1.0 / math.sqrt(128)
+    if not math.isfinite(softmax_scale) or softmax_scale <= 0.0:
+        raise ValueError("ExpCast requires a positive finite softmax_scale")
+
+    q, k = q.contiguous(), k.contiguous()
+    batch = q.shape[0] if q.ndim == 4 else 1
+    sq, heads = q.shape[-3], q.shape[-2]
+    sk = k.shape[-3]
+    if k.shape[-2] != heads or (q.ndim == 4 and k.shape[0] != batch):
+        raise ValueError("Q and K must agree on batch and heads (MHA)")
+    if v_prepacked and batch != 1:
+        raise ValueError("v_prepacked requires a single-sequence [S,H,128] view")
+    if tuple(v.shape[-3:]) != (sk, heads, 128):
+        raise ValueError("K and V shapes must match")
+    device = q.device
+    for t, name, shape in (
+        (q_descale, "q_descale", (batch, heads)),
+        (k_descale, "k_descale", (batch, heads)),
+    ):
+        if t.dtype != torch.float32 or t.device != device or t.dim() != 3 or tuple(t.shape[:2]) != shape:
+            raise ValueError(f"{name} must be float32 [batch, heads, blocks] on the input device")
+    k_blocks = (sk + 127) // 128
+    if q_descale.shape[2] < (sq + 127) // 128 or k_descale.shape[2] != k_blocks:
+        raise ValueError("descale block counts do not match the sequence lengths")
+    if v_descale.dtype != torch.float32 or v_descale.device != device or tuple(v_descale.shape) != (batch, heads):
+        raise ValueError("v_descale must be float32 [batch, heads] on the input device")
+    repair_rows = 0
+    if repair_k_descale is not None:
+        # src/open_vc_attn/_kernels/blackwell/flash_attn/cute/interface.py:538-558
+        rows = repair_k_descale.shape[-1] if repair_k_descale.dim() == 3 else 0
+        if (
+            repair_k_descale.dim() != 3
+            or tuple(repair_k_descale.shape[:2]) != (batch, heads)
+            or rows == 0
+            or rows % 128 != 0
+            or rows >= sk
+            or repair_k_descale.dtype != torch.float32
+            or repair_k_descale.device != device
+            or not repair_k_descale.is_contiguous()
+            or batch != 1
+        ):
+            raise ValueError(
+                "repair_k_descale must be contiguous float32 [batch, kv_heads, R] on the "
+                f"input device with 0 < R < {sk} and R a multiple of 128"
+            )
+        repair_rows = rows
+    window = -1 if mid_window_blocks is None else int(mid_window_blocks)
+    if window < -1:
+        raise ValueError("mid_window_blocks must be None or >= 0")
+
+    lib = _lib.load()
+    with torch.cuda.device(device):
+        if v_prepacked:
+            packed_ptr = v.data_ptr()
+            keep = v
+        else:
+            from .quantization import pack_v
+
+            keep = pack_v(v.contiguous())
+            packed_ptr = keep.data_ptr()
+        out = torch.empty(q.shape, dtype=torch.bfloat16, device=device)
+        q_descale, k_descale, v_descale = q_descale.contiguous(), k_descale.contiguous(), v_descale.contiguous()
+        _lib.check(
+            lib.ovc_attention(
+                q.data_ptr(), k.data_ptr(), packed_ptr, q_descale.data_ptr(), q_descale.shape[2],
+                k_descale.data_ptr(), v_descale.data_ptr(),
+                None if repair_k_descale is None else repair_k_descale.data_ptr(), repair_rows,
+                out.data_ptr(), batch, sq, sk, heads, float(softmax_scale), window,
+                status_word(device).data_ptr(), _lib.stream_pointer(device),
+            ),
+            "ovc_attention",
+        )
+        del keep
+    return out, None
+
+
+_flash_attn_fwd = flash_attn_fwd
