@@ -52,7 +52,8 @@ def build(verbose=False, force=False):
             cmd.insert(1, "-Xptxas=-v")
         subprocess.run(cmd, check=True)
         objects.append(obj)
-    subprocess.run([nvcc_path(), "-shared", "-o", out, *objects, "-lcudart"], check=True)
+    subprocess.run([nvcc_path(), "-gencode", "arch=compute_100a,code=sm_100a", "-shared", "-o", out, *objects, "-lcudart"],
+                   check=True)
     return out
 
 

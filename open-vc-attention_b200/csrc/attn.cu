@@ -2,17 +2,30 @@
 // accumulators in tensor memory, score -> FP8 probability conversion on CUDA cores.
 //
 // One CTA owns 256 query rows of one (batch, head): two 128-row stages that ping-pong through one
-// score buffer in tensor memory.  Warp roles: warps 0-3 convert scores of stage 0, warps 4-7 of
-// stage 1, warp 8 issues TMA loads, warp 9 issues MMAs; warps 10-11 only take part in register
-// reallocation.  Numerics follow the reference's packed kernel
+// score buffer in tensor memory.  Numerics follow the reference's packed kernel
 // (src/open_vc_attn/_kernels/blackwell/flash_attn/cute/flash_fwd_sm100.py:3513-3911 with
 // cute/softmax.py:203-248 and cute/utils.py:704-795): running max in the descaled domain,
 // ExpCast codes from one FMA and an FP16-subnormal rounding, denominator summed by the tensor core
 // through a block of ones appended to the V tile.
 //
+// Warp roles (384 threads): warps 0-3 convert the scores of stage 0 (one query row per thread),
+// warps 4-7 those of stage 1, warp 8 issues TMA loads, warp 9 issues MMAs, warp 10 relays "tile
+// landed" from the TMA barriers into the MMA gate, warp 11 only takes part in register reallocation.
+//
+// Schedule.  Issuing an MMA group blocks the issuing thread for about as long as the group runs,
+// and every barrier wait and tcgen05.commit in that thread costs tensor-pipe idle time, so the MMA
+// warp is given the fewest possible of both.  Per key step n it issues two groups,
+//     gate0 -> S = Q0 K(n)^T, commit, O0 += P0(n-1) [V(n-1) | 1], commit
+//     gate1 -> S = Q1 K(n)^T, commit, O1 += P1(n-1) [V(n-1) | 1], commit
+// where gate0 collects "P0(n-1) stored" from stage 0, "S1(n-1) copied out" from stage 1 and
+// "V(n-1), K(n) landed" from the relay, and gate1 collects "S0(n) copied out" and "P1(n-1) stored".
+// QK is issued before the PV of the same stage so that the next scores are ready when the
+// conversion warps come back.  Shared-memory slots are recycled from progress counters that the
+// conversion warps publish, not from extra commits.
+//
 // Tensor memory map (512 columns): S 0..127 (shared by both stages), P0 128..159, P1 160..191,
-// O0 192..335, O1 336..479; each O region is 128 output columns followed by 16 copies of the
-// denominator (the PV product has N = 144).
+// O0 192..327, O1 328..463; each O region is 128 output columns followed by 8 copies of the
+// denominator (the PV product has N = 136).
 
 #include <cuda.h>
 #include <cuda_bf16.h>
@@ -27,25 +40,29 @@ namespace {
 using namespace ptx;
 
 constexpr int kThreads = 384;
-constexpr int kKStages = 3;
-constexpr int kVStages = 3;
+constexpr int kKStages = 4;
+constexpr int kVStages = 4;
 constexpr int kTileBytes = kTile * kDim;          // 16384: one FP8 tile, 128 rows of 128 bytes
-constexpr int kOnesRows = 16;                     // extension of the PV product that sums P
+constexpr int kOnesRows = 8;                      // extension of the PV product that sums P
 constexpr int kVSlotBytes = kTileBytes + kOnesRows * 128;
-constexpr int kPvN = kDim + kOnesRows;            // 144
-constexpr uint32_t kColS = 0, kColP = 128, kColO = 192, kColOStride = 144, kTmemCols = 512;
+constexpr int kPvN = kDim + kOnesRows;            // 136
+constexpr uint32_t kColS = 0, kColP = 128, kColO = 192, kColOStride = kPvN, kTmemCols = 512;
 constexpr long long kWaitCycles = 400000000LL;    // bounded barrier wait (~0.2 s)
+constexpr uint32_t kSleepHintNs = 100000;         // one hardware-suspended try_wait lasts at most this
 
 struct SmemLayout {
     alignas(1024) uint8_t q[2][kTileBytes];
     alignas(1024) uint8_t k[kKStages][kTileBytes];
     alignas(1024) uint8_t v[kVStages][kVSlotBytes];
     alignas(8) uint64_t q_full[2];
-    uint64_t k_full[kKStages], k_empty[kKStages];
-    uint64_t v_full[kVStages], v_empty[kVStages];
-    uint64_t s_full[2], s_empty, p_full[2], o_full[2], drain;
+    uint64_t k_full[kKStages], v_full[kVStages];
+    uint64_t s_full[2];   // scores of a stage are in tensor memory (commit)
+    uint64_t gate[2];     // what the MMA warp waits for before a stage's group
+    uint64_t pv_done[2];  // the stage's previous PV has been accumulated (commit)
+    uint64_t o_full[2], drain;
     uint32_t tmem_base;
     volatile uint32_t abort_flag;
+    volatile int progress[2];  // progress[s] = number of s_full[s] phases observed by stage s
 };
 
 struct AttnParams {
@@ -70,6 +87,11 @@ __device__ __forceinline__ int tile_at(int it, int j0, int first_tile, int n_til
     return first_tile - 1 - (it - originals);
 }
 
+__device__ __forceinline__ void give_up(SmemLayout& sm, uint32_t* status) {
+    sm.abort_flag = 1;
+    if (status != nullptr) atomicOr(status, OVC_STATUS_WAIT_EXPIRED);
+}
+
 // Bounded wait.  Returns false when the barrier did not complete in time or another thread of
 // the CTA already gave up; the caller then leaves its loop and the CTA tears down.
 __device__ __forceinline__ bool wait_bar(SmemLayout& sm, uint64_t* bar, uint32_t parity, uint32_t* status) {
@@ -77,19 +99,45 @@ __device__ __forceinline__ bool wait_bar(SmemLayout& sm, uint64_t* bar, uint32_t
     if (mbar_try_wait(addr, parity)) return true;
     const long long start = clock64();
     while (true) {
-        if (mbar_try_wait(addr, parity)) return true;
+        if (mbar_try_wait_sleep(addr, parity, kSleepHintNs)) return true;
         if (sm.abort_flag) return false;
         if (clock64() - start > kWaitCycles) {
-            sm.abort_flag = 1;
-            if (status != nullptr) atomicOr(status, OVC_STATUS_WAIT_EXPIRED);
+            give_up(sm, status);
             return false;
         }
     }
 }
 
+// Bounded wait until a progress counter reaches `target`.
+__device__ __forceinline__ bool wait_progress(SmemLayout& sm, int which, int target, uint32_t* status) {
+    if (sm.progress[which] >= target) return true;
+    const long long start = clock64();
+    while (sm.progress[which] < target) {
+        if (sm.abort_flag) return false;
+        if (clock64() - start > kWaitCycles) {
+            give_up(sm, status);
+            return false;
+        }
+        __nanosleep(64);
+    }
+    return true;
+}
+
 #ifdef OVC_DEBUG_DUMP
 // Debug builds only: raw scores and codes of CTA 0's first key tile go to this buffer.
 __device__ float* g_debug_dump = nullptr;
+// Timeline stamps (%clock) of CTA 0's first 64 steps: [step][32 slots]; tl_base is a register copy
+// of the buffer pointer so that a stamp costs one special-register read and one store.
+#define OVC_TL(step, slot)                                                                  \
+    do {                                                                                    \
+        if (tl_base != nullptr && (step) >= 256 && (step) < 320 && lane == 0) {             \
+            uint32_t now;                                                                   \
+            asm volatile("mov.u32 %0, %%clock;" : "=r"(now));                               \
+            tl_base[((step) - 256) * 32 + (slot)] = now;                                    \
+        }                                                                                   \
+    } while (0)
+#else
+#define OVC_TL(step, slot) do {} while (0)
 #endif
 
 __device__ __forceinline__ float fmax3(float a, float b, float c) {
@@ -152,6 +200,10 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
     if (skip_cta != 0) return;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+#ifdef OVC_DEBUG_DUMP
+    uint32_t* const tl_base = (g_debug_dump != nullptr && blockIdx.x == 0)
+                                  ? reinterpret_cast<uint32_t*>(g_debug_dump) + 256 * 128 + 256 * 32 : nullptr;
+#endif
     const int m_block = blockIdx.x % p.m_blocks;
     const int bh = blockIdx.x / p.m_blocks;
     const int head = bh % p.H, batch = bh / p.H;
@@ -163,23 +215,20 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         for (int i = 0; i < 2; ++i) {
             mbar_init(smem_addr(&sm.q_full[i]), 1);
             mbar_init(smem_addr(&sm.s_full[i]), 1);
-            mbar_init(smem_addr(&sm.p_full[i]), 128);
+            mbar_init(smem_addr(&sm.pv_done[i]), 1);
             mbar_init(smem_addr(&sm.o_full[i]), 1);
         }
-        for (int i = 0; i < kKStages; ++i) {
-            mbar_init(smem_addr(&sm.k_full[i]), 1);
-            mbar_init(smem_addr(&sm.k_empty[i]), 1);
-        }
-        for (int i = 0; i < kVStages; ++i) {
-            mbar_init(smem_addr(&sm.v_full[i]), 1);
-            mbar_init(smem_addr(&sm.v_empty[i]), 1);
-        }
-        mbar_init(smem_addr(&sm.s_empty), 128);
+        for (int i = 0; i < kKStages; ++i) mbar_init(smem_addr(&sm.k_full[i]), 1);
+        for (int i = 0; i < kVStages; ++i) mbar_init(smem_addr(&sm.v_full[i]), 1);
+        mbar_init(smem_addr(&sm.gate[0]), 257);  // 128 + 128 conversion threads + the relay
+        mbar_init(smem_addr(&sm.gate[1]), 256);
         mbar_init(smem_addr(&sm.drain), 1);
         sm.abort_flag = 0;
+        sm.progress[0] = 0;
+        sm.progress[1] = 0;
         mbar_init_fence();
     }
-    // Rows 128..143 of every V slot: E4M3 1.0, so PV also accumulates the row sums of P.
+    // Rows 128.. of every V slot: E4M3 1.0, so PV also accumulates the row sums of P.
     for (int i = threadIdx.x; i < kVStages * kOnesRows * 128 / 4; i += kThreads) {
         const int slot = i / (kOnesRows * 128 / 4), w = i % (kOnesRows * 128 / 4);
         reinterpret_cast<uint32_t*>(&sm.v[slot][kTileBytes])[w] = 0x38383838u;
@@ -208,35 +257,37 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
                     tma_load_4d(smem_addr(sm.q[s]), &tmap_q, smem_addr(&sm.q_full[s]), 0, head,
                                 (2 * m_block + s) * kTile, batch, stream);
                 }
-                int it = 0;
-                for (; it < n_iters; ++it) {
+                int issued_k = 0, issued_v = 0;
+                for (int it = 0; it < n_iters; ++it) {
                     const int j = tile_at(it, j0, p.first_tile, p.n_tiles);
                     const int ks = it % kKStages, vs = it % kVStages;
-                    if (!wait_bar(sm, &sm.k_empty[ks], ((it / kKStages) & 1) ^ 1, p.status)) break;
+                    // K(it - kKStages) was last read by stage 1's QK of that step.
+                    if (!wait_progress(sm, 1, it - kKStages + 1, p.status)) break;
                     mbar_expect_tx(smem_addr(&sm.k_full[ks]), kTileBytes);
                     tma_load_4d(smem_addr(sm.k[ks]), &tmap_k, smem_addr(&sm.k_full[ks]), 0, head, j * kTile, batch, keep);
-                    if (!wait_bar(sm, &sm.v_empty[vs], ((it / kVStages) & 1) ^ 1, p.status)) break;
+                    issued_k = it + 1;
+                    // V(it - kVStages) was last read by stage 1's PV, which the commit after stage 0's
+                    // QK two steps later covers.
+                    if (!wait_progress(sm, 0, it - kVStages + 3, p.status)) break;
                     mbar_expect_tx(smem_addr(&sm.v_full[vs]), kTileBytes);
                     tma_load_4d(smem_addr(sm.v[vs]), &tmap_v, smem_addr(&sm.v_full[vs]), j * kTile, 0, head, batch, keep);
+                    issued_v = it + 1;
                 }
                 if (sm.abort_flag) {
                     // Give the copies already issued a bounded time to land before the CTA exits.
-                    const int issued_k = min(it + 1, n_iters), issued_v = it;
                     for (int s = 0; s < kKStages; ++s) {
-                        const int last = issued_k - 1 - ((issued_k - 1 - s) % kKStages + kKStages) % kKStages;
-                        if (issued_k > 0 && last >= 0) {
-                            const long long t0 = clock64();
-                            while (!mbar_try_wait(smem_addr(&sm.k_full[s]), (last / kKStages) & 1) &&
-                                   clock64() - t0 < kWaitCycles) {}
-                        }
+                        int last = issued_k - 1;
+                        while (last >= 0 && last % kKStages != s) --last;
+                        const long long t0 = clock64();
+                        while (last >= 0 && !mbar_try_wait(smem_addr(&sm.k_full[s]), (last / kKStages) & 1) &&
+                               clock64() - t0 < kWaitCycles) {}
                     }
                     for (int s = 0; s < kVStages; ++s) {
-                        const int last = issued_v - 1 - ((issued_v - 1 - s) % kVStages + kVStages) % kVStages;
-                        if (issued_v > 0 && last >= 0) {
-                            const long long t0 = clock64();
-                            while (!mbar_try_wait(smem_addr(&sm.v_full[s]), (last / kVStages) & 1) &&
-                                   clock64() - t0 < kWaitCycles) {}
-                        }
+                        int last = issued_v - 1;
+                        while (last >= 0 && last % kVStages != s) --last;
+                        const long long t0 = clock64();
+                        while (last >= 0 && !mbar_try_wait(smem_addr(&sm.v_full[s]), (last / kVStages) & 1) &&
+                               clock64() - t0 < kWaitCycles) {}
                     }
                     const long long t0 = clock64();
                     while (!(mbar_try_wait(smem_addr(&sm.q_full[0]), 0) && mbar_try_wait(smem_addr(&sm.q_full[1]), 0)) &&
@@ -247,49 +298,48 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
             // ---------------- MMA issuer ----------------
             constexpr uint32_t idesc_qk = idesc_e4m3_f32(kTile);
             constexpr uint32_t idesc_pv = idesc_e4m3_f32(kPvN);
-            bool ok = wait_bar(sm, &sm.q_full[0], 0, p.status) && wait_bar(sm, &sm.q_full[1], 0, p.status);
+            bool ok = wait_bar(sm, &sm.q_full[0], 0, p.status) && wait_bar(sm, &sm.q_full[1], 0, p.status) &&
+                      wait_bar(sm, &sm.k_full[0], 0, p.status);
             ok = __all_sync(0xFFFFFFFFu, ok);
-            for (int it = 0; ok && it <= n_iters; ++it) {
-                const int ks = it % kKStages;
-                if (it < n_iters) ok = wait_bar(sm, &sm.k_full[ks], (it / kKStages) & 1, p.status);
-                const int pv = it - 1, vs = (pv + kVStages) % kVStages;
-                if (ok && it > 0) ok = wait_bar(sm, &sm.v_full[vs], (pv / kVStages) & 1, p.status);
-                ok = __all_sync(0xFFFFFFFFu, ok);
-                for (int s = 0; ok && s < 2; ++s) {
-                    if (it > 0) {
-                        // O[s] (+)= P[s] * [V | 1]
-                        ok = __all_sync(0xFFFFFFFFu, wait_bar(sm, &sm.p_full[s], pv & 1, p.status));
+            // Step n: stage s gets S = Q[s] K(n)^T and then O[s] += P[s](n-1) [V(n-1) | 1].
+            for (int n = 0; ok && n <= n_iters; ++n) {
+                const int it = n;
+                const uint64_t kdesc = smem_desc_sw128(smem_addr(sm.k[n % kKStages]));
+                const uint64_t vdesc = smem_desc_sw128(smem_addr(sm.v[(n + kVStages - 1) % kVStages]));
+                for (int s = 0; s < 2; ++s) {
+                    if (n > 0 || s == 1) {
+                        // gate[0] completion n-1 / gate[1] completion n
+                        OVC_TL(it, 12 + s * 6 + 0);
+                        ok = __all_sync(0xFFFFFFFFu, wait_bar(sm, &sm.gate[s], (n - 1 + s) & 1, p.status));
                         if (!ok) break;
                         tc_fence_after();
-                        if (lane == 0) {
-                            const uint64_t b = smem_desc_sw128(smem_addr(sm.v[vs]));
+                        OVC_TL(it, 12 + s * 6 + 1);
+                    }
+                    if (lane == 0) {
+                        if (n < n_iters) {
+                            const uint64_t a = smem_desc_sw128(smem_addr(sm.q[s]));
+#pragma unroll
+                            for (int kk = 0; kk < 4; ++kk) {
+                                mma_f8_ss(tmem + kColS, a + 2 * kk, kdesc + 2 * kk, idesc_qk, kk > 0 ? 1u : 0u);
+                                if (s == 0) OVC_TL(it, 24 + kk);
+                            }
+                            mma_commit(smem_addr(&sm.s_full[s]));
+                            if (s == 0) OVC_TL(it, 28);
+                        }
+                        if (n > 0) {
                             const uint32_t d = tmem + kColO + s * kColOStride, a = tmem + kColP + 32 * s;
 #pragma unroll
-                            for (int kk = 0; kk < 4; ++kk)
-                                mma_f8_ts(d, a + 8 * kk, b + 2 * kk, idesc_pv, (pv > 0 || kk > 0) ? 1u : 0u);
-                            if (s == 1) mma_commit(smem_addr(&sm.v_empty[vs]));
-                            if (it == n_iters) mma_commit(smem_addr(&sm.o_full[s]));
+                            for (int kk = 0; kk < 4; ++kk) {
+                                mma_f8_ts(d, a + 8 * kk, vdesc + 2 * kk, idesc_pv, (n > 1 || kk > 0) ? 1u : 0u);
+                                if (s == 0 && kk == 1) OVC_TL(it, 29);
+                                if (s == 0 && kk == 3) OVC_TL(it, 30);
+                            }
+                            mma_commit(smem_addr(n < n_iters ? &sm.pv_done[s] : &sm.o_full[s]));
+                            if (s == 0) OVC_TL(it, 31);
                         }
-                        __syncwarp();
                     }
-                    if (it < n_iters) {
-                        // S = Q[s] * K^T once the previous scores have left tensor memory
-                        if (it > 0 || s > 0) {
-                            ok = __all_sync(0xFFFFFFFFu, wait_bar(sm, &sm.s_empty, (2 * it + s - 1) & 1, p.status));
-                            if (!ok) break;
-                            tc_fence_after();
-                        }
-                        if (lane == 0) {
-                            const uint64_t a = smem_desc_sw128(smem_addr(sm.q[s]));
-                            const uint64_t b = smem_desc_sw128(smem_addr(sm.k[ks]));
-#pragma unroll
-                            for (int kk = 0; kk < 4; ++kk)
-                                mma_f8_ss(tmem + kColS, a + 2 * kk, b + 2 * kk, idesc_qk, kk > 0 ? 1u : 0u);
-                            mma_commit(smem_addr(&sm.s_full[s]));
-                            if (s == 1) mma_commit(smem_addr(&sm.k_empty[ks]));
-                        }
-                        __syncwarp();
-                    }
+                    __syncwarp();
+                    OVC_TL(it, 12 + s * 6 + 2);
                 }
             }
             if (!ok) {
@@ -298,6 +348,19 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
                 __syncwarp();
                 const long long t0 = clock64();
                 while (!mbar_try_wait(smem_addr(&sm.drain), 0) && clock64() - t0 < kWaitCycles) {}
+            }
+        } else if (warp == 10) {
+            // ---------------- relay: TMA arrivals -> gate[0] ----------------
+            // gate[0] completion k lets the MMA warp issue QK with K(k+1) and PV with V(k).
+            if (lane == 0) {
+                for (int k = 0; k < n_iters; ++k) {
+                    if (!wait_bar(sm, &sm.v_full[k % kVStages], (k / kVStages) & 1, p.status)) break;
+                    if (k + 1 < n_iters &&
+                        !wait_bar(sm, &sm.k_full[(k + 1) % kKStages], ((k + 1) / kKStages) & 1, p.status))
+                        break;
+                    if (k > 0 && !wait_bar(sm, &sm.gate[0], (k - 1) & 1, p.status)) break;
+                    mbar_arrive(smem_addr(&sm.gate[0]));
+                }
             }
         }
     } else {
@@ -315,15 +378,23 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         const float code_scale0 = sigma * 4.76837158203125e-07f;  // sigma * 8 * 2^-24
         const float* kd_row = p.k_descale + bh_l * p.n_tiles;
         const int tail_valid = static_cast<int>(p.Sk - static_cast<long long>(p.n_tiles - 1) * kTile);
+        const uint32_t gate_copied = smem_addr(&sm.gate[1 - stage]);  // "my scores left tensor memory"
+        const uint32_t gate_stored = smem_addr(&sm.gate[stage]);      // "my probabilities are stored"
+
+        // gate[1] completion 0 has no "P1(-1) stored": stage 1 supplies those arrivals up front.
+        if (stage == 1) mbar_arrive(gate_stored);
 
         float row_max = 0.0f, saved_denominator = 0.0f;
         bool ok = true;
         for (int it = 0; it < n_iters; ++it) {
             const int j = tile_at(it, j0, p.first_tile, p.n_tiles);
             const float kd = __ldg(kd_row + j);
+            if ((warp & 3) == 0) OVC_TL(it, stage * 6 + 0);
             ok = __all_sync(0xFFFFFFFFu, wait_bar(sm, &sm.s_full[stage], it & 1, p.status));
             if (!ok) break;
+            if ((warp & 3) == 0) OVC_TL(it, stage * 6 + 1);
             tc_fence_after();
+            if ((warp & 3) == 0 && lane == 0) sm.progress[stage] = it + 1;
             uint32_t s[128];
             tmem_ld32(t_s, s);
             tmem_ld32(t_s + 32, s + 32);
@@ -331,7 +402,8 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
             tmem_ld32(t_s + 96, s + 96);
             tmem_wait_ld();
             tc_fence_before();
-            mbar_arrive(smem_addr(&sm.s_empty));
+            mbar_arrive(gate_copied);
+            if ((warp & 3) == 0) OVC_TL(it, stage * 6 + 2);
 
 #ifdef OVC_DEBUG_DUMP
             if (g_debug_dump != nullptr && blockIdx.x == 0 && it == 0) {
@@ -371,6 +443,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
             for (int c = 0; c < 5; ++c) m1[c] = fmax3(m3[3 * c], m3[3 * c + 1], m3[3 * c + 2]);
             const float tile_max = fmaxf(fmax3(m1[0], m1[1], m1[2]), fmaxf(m1[3], m1[4])) * kd;
 
+            if ((warp & 3) == 0) OVC_TL(it, stage * 6 + 3);
             float alpha = 0.0f;
             float new_max = tile_max;
             if (it > 0) {
@@ -387,6 +460,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
 #pragma unroll
             for (int c = 0; c < 32; ++c) codes[c] = encode4(s[4 * c], s[4 * c + 1], s[4 * c + 2], s[4 * c + 3], scale2, bias2);
             tmem_st32(t_p, codes);
+            if ((warp & 3) == 0) OVC_TL(it, stage * 6 + 4);
 #ifdef OVC_DEBUG_DUMP
             if (g_debug_dump != nullptr && blockIdx.x == 0 && it == 0) {
                 uint32_t* d = reinterpret_cast<uint32_t*>(g_debug_dump) + 256 * 128 + (stage * 128 + row_in_tile) * 32;
@@ -394,12 +468,20 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
             }
 #endif
 
-            if (p.first_tile > 0 && j == p.first_tile - 1) {
+            const bool first_repair = p.first_tile > 0 && j == p.first_tile - 1;
+            const bool rescale = it > 0 && __any_sync(0xFFFFFFFFu, alpha < 1.0f);
+            if (first_repair || rescale) {
+                // Both touch this stage's accumulator: its previous PV (step it-1) must have landed.
+                ok = __all_sync(0xFFFFFFFFu, wait_bar(sm, &sm.pv_done[stage], (it - 1) & 1, p.status));
+                if (!ok) break;
+                tc_fence_after();
+            }
+            if (first_repair) {
                 // First repair tile: the denominator holds the original tokens' total only.
                 saved_denominator = __uint_as_float(tmem_ld1(t_o + kDim));
                 tmem_wait_ld();
             }
-            if (it > 0 && __any_sync(0xFFFFFFFFu, alpha < 1.0f)) {
+            if (rescale) {
                 // The running max moved: rescale the accumulator and the denominator in place.
 #pragma unroll
                 for (int c = 0; c < 4; ++c) {
@@ -416,8 +498,11 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
             }
             tmem_wait_st();
             tc_fence_before();
-            mbar_arrive(smem_addr(&sm.p_full[stage]));
+            mbar_arrive(gate_stored);
+            if ((warp & 3) == 0) OVC_TL(it, stage * 6 + 5);
         }
+        // gate[1]'s last completion has no "S0 copied out": stage 0 supplies those arrivals.
+        if (ok && stage == 0) mbar_arrive(gate_copied);
         if (ok) ok = __all_sync(0xFFFFFFFFu, wait_bar(sm, &sm.o_full[stage], 0, p.status));
         if (ok) {
             tc_fence_after();

@@ -1,0 +1,62 @@
+"""Helpers shared by the GPU parity tests."""
+
+import numpy as np
+import torch
+
+from oracle import attention as oatt
+from oracle import prep as oprep
+
+DEV = "cuda:0"
+
+
+def u8(t):
+    return t.contiguous().view(torch.uint8).cpu().numpy()
+
+
+def f32(t):
+    return t.float().cpu().numpy()
+
+
+def packed_buffer(view):
+    """The [H,128,S_pad] buffer behind a prepacked [S,H,128] view."""
+    s, h, d = view.shape
+    padded = (s + 127) // 128 * 128
+    flat = torch.empty(0, dtype=torch.uint8, device=view.device).set_(view.untyped_storage(), 0, (h, d, padded))
+    return flat.cpu().numpy()
+
+
+def structured_qkv(s, h, seed, dtype=torch.bfloat16, device=DEV):
+    """Synthetic stand-in for the video-DiT captures: Q,K ~ N(0,1) with 4 of 128 channels per head
+    scaled x8 and a LogNormal(0,0.3) per-token norm; V ~ N(mu_h,1) with per-head channel means
+    mu_h ~ N(0,2)."""
+    g = torch.Generator(device=device).manual_seed(seed)
+    q = torch.randn(s, h, 128, generator=g, device=device)
+    k = torch.randn(s, h, 128, generator=g, device=device)
+    for t in (q, k):
+        for head in range(h):
+            idx = torch.randperm(128, generator=g, device=device)[:4]
+            t[:, head, idx] *= 8
+        t *= torch.exp(0.3 * torch.randn(s, 1, 1, generator=g, device=device))
+    mu = 2.0 * torch.randn(1, h, 128, generator=g, device=device)
+    v = torch.randn(s, h, 128, generator=g, device=device) + mu
+    return q.to(dtype), k.to(dtype), v.to(dtype)
+
+
+def oracle_rows(prepared, m_blocks, heads, window=4, repair_kd=None):
+    """Oracle output for the query rows of the given 256-row blocks and heads, from prepared FP8
+    tensors (packed or row-major V).  Returns (rows index array, float32 [len(rows), len(heads), 128])."""
+    q8, k8 = u8(prepared.q), u8(prepared.k)
+    s_k = k8.shape[0]
+    if getattr(prepared, "v_prepacked", False):
+        v8 = packed_buffer(prepared.v)[:, :, :s_k].transpose(2, 0, 1)
+    else:
+        v8 = u8(prepared.v)
+    heads = list(heads)
+    out = oatt.expcast_attention(
+        q8[:, heads], k8[:, heads], np.ascontiguousarray(v8[:, heads]),
+        f32(prepared.q_descale)[0][heads], f32(prepared.k_descale)[0][heads], f32(prepared.v_descale)[0][heads],
+        mid_window_blocks=window, rows=list(m_blocks),
+        repair_k_descale=None if repair_kd is None else f32(repair_kd)[0][heads],
+    )
+    rows = np.concatenate([np.arange(256 * m, min(256 * m + 256, q8.shape[0])) for m in m_blocks])
+    return rows, out[rows]

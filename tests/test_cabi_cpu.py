@@ -1,0 +1,70 @@
+"""The C-ABI library: it loads, exports everything include/ovc.h declares, and rejects bad
+arguments before touching a GPU."""
+
+import ctypes
+import os
+import re
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.fixture(scope="module")
+def lib():
+    import __graft_entry__
+
+    __graft_entry__.build()
+    from open_vc_attn import _lib
+
+    return _lib.load()
+
+
+def declared_functions():
+    text = open(os.path.join(ROOT, "include", "ovc.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(ovc_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_header_declares_the_path():
+    names = declared_functions()
+    for needed in ("ovc_prepare_fused", "ovc_quantize_per_block", "ovc_quantize_per_head", "ovc_head_amax",
+                   "ovc_pack_v", "ovc_repair_score", "ovc_repair_rows", "ovc_attention"):
+        assert needed in names
+
+
+def test_every_declared_symbol_is_exported_and_bound(lib):
+    from open_vc_attn import _lib
+
+    for name in declared_functions():
+        assert hasattr(lib, name), name
+        assert name in _lib.SIGNATURES, f"{name} has no ctypes signature"
+    assert lib.ovc_version() >= 1
+    assert lib.ovc_error_string(0) == b"ok"
+    assert b"argument" in lib.ovc_error_string(-1)
+
+
+def test_null_and_bad_arguments_are_rejected_without_a_gpu(lib):
+    null = None
+    bad = -1
+    assert lib.ovc_quantize_per_block(null, 1, 1, 128, 1, null, null, 1, null) == bad
+    assert lib.ovc_head_amax(null, 1, 1, 128, 1, null, null) == bad
+    assert lib.ovc_quantize_per_head(null, 1, 1, 128, 1, null, null, null, null) == bad
+    assert lib.ovc_prepare_fused(null, null, null, 1, 128, 1, null, null, null, null, null, null, null, null) == bad
+    assert lib.ovc_pack_v(null, 1, 128, 1, null, null) == bad
+    assert lib.ovc_repair_score(null, 1, 128, 1, null, null, null, null) == bad
+    assert lib.ovc_repair_rows(null, null, null, 1, null, null, null, null, 1, 128, 128, 1, 1, null) == bad
+    assert lib.ovc_attention(null, null, null, null, 1, null, null, null, 0, null, 1, 128, 128, 1, 0.1, 4, null, null) == bad
+    # non-null but otherwise invalid: sizes, dtype, alignment, scale
+    buf = ctypes.create_string_buffer(4096)
+    p = ctypes.addressof(buf) // 16 * 16 + 16
+    assert lib.ovc_quantize_per_block(p, 7, 1, 128, 1, p, p, 1, null) == bad          # dtype
+    assert lib.ovc_quantize_per_block(p, 1, 1, 0, 1, p, p, 1, null) == bad            # S = 0
+    assert lib.ovc_quantize_per_block(p, 1, 1, 300, 1, p, p, 2, null) == bad          # descale row too short
+    assert lib.ovc_quantize_per_block(p + 2, 1, 1, 128, 1, p, p, 1, null) == bad      # misaligned input
+    assert lib.ovc_attention(p, p, p, p, 1, p, p, null, 0, p, 1, 128, 128, 1, 0.0, 4, null, null) == bad   # scale
+    assert lib.ovc_attention(p, p, p, p, 1, p, p, null, 0, p, 1, 128, 128, 1, float("nan"), 4, null, null) == bad
+    assert lib.ovc_attention(p, p, p, p, 1, p, p, null, 128, p, 1, 128, 256, 1, 0.1, 4, null, null) == bad  # repair w/o kd
+    assert lib.ovc_attention(p, p, p, p, 1, p, p, p, 100, p, 1, 128, 256, 1, 0.1, 4, null, null) == bad     # R % 128
+    assert lib.ovc_attention(p, p, p, p, 0, p, p, null, 0, p, 1, 128, 128, 1, 0.1, 4, null, null) == bad    # q_blocks
+    assert lib.ovc_attention(p, p, p, p, 1, p, p, null, 0, p, 1, 128, 128, 1, 0.1, -2, null, null) == bad   # window

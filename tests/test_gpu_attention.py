@@ -1,0 +1,196 @@
+"""ExpCast attention on the GPU against the CPU oracle (rel-L2 <= 0.5 %, the bound set for agreement
+with the reference's ExpCast output) and exact attention (< 10 %, the reference's own smoke bound)."""
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import attention as oatt
+from oracle import prep as oprep
+
+pytestmark = pytest.mark.gpu
+
+from gpu_util import DEV, f32, oracle_rows, structured_qkv, u8  # noqa: E402
+
+ORACLE_TOL = 5e-3
+
+
+def _api():
+    import open_vc_attn
+    from open_vc_attn import api, forward
+
+    return open_vc_attn, api, forward
+
+
+def oracle_full(q, k, v, window=4, softmax_scale=None, encoder="packed"):
+    qf, kf, vf = (f32(t) for t in (q, k, v))
+    batched = qf.ndim == 4
+    if not batched:
+        qf, kf, vf = qf[None], kf[None], vf[None]
+    pq, pk, pv = oprep.quantize_per_block(qf), oprep.quantize_per_block(kf), oprep.quantize_per_head(vf)
+    outs = [
+        oatt.expcast_attention(pq[0][b], pk[0][b], pv[0][b], pq[1][b], pk[1][b], pv[1][b], mid_window_blocks=window,
+                               softmax_scale=softmax_scale, encoder=encoder)
+        for b in range(qf.shape[0])
+    ]
+    out = np.stack(outs)
+    return out if batched else out[0]
+
+
+@pytest.mark.parametrize("s", [1, 129, 1024])
+def test_small_sequences_match_oracle_and_exact_attention(s):
+    # shapes and seeds of tests/gpu/test_attention.py:27-39 of the reference
+    ovc, api, forward = _api()
+    torch.manual_seed(700 + s)
+    q, k, v = [torch.randn(s, 2, 128, device=DEV, dtype=torch.bfloat16) for _ in range(3)]
+    out = ovc.attention(q, k, v)
+    forward.check_status(q.device)
+    assert out.dtype == torch.bfloat16 and out.shape == q.shape
+    assert torch.equal(out, ovc.attention(q, k, v))  # bit-repeatable
+    got = f32(out)
+    assert oatt.relative_l2(got, oracle_full(q, k, v)) < ORACLE_TOL
+    assert oatt.relative_l2(got, oracle_full(q, k, v, encoder="general")) < ORACLE_TOL
+    assert oatt.relative_l2(got, oatt.exact_attention(f32(q), f32(k), f32(v))) < 0.10
+
+
+@pytest.mark.parametrize("s,h,window", [(127, 1, 4), (128, 3, 4), (255, 2, None), (257, 2, 4), (640, 1, 0), (1500, 2, 2),
+                                        (1500, 2, None), (4096, 4, 4)])
+def test_tile_counts_tails_and_scan_orders(s, h, window):
+    """1, 2, 3, 5, ... key tiles, tails on both sides of a tile edge, every traversal option."""
+    ovc, api, forward = _api()
+    g = torch.Generator(device=DEV).manual_seed(s * 7 + h)
+    q, k, v = [torch.randn(s, h, 128, generator=g, device=DEV).to(torch.float16) for _ in range(3)]
+    out = ovc.attention(q, k, v, mid_window_blocks=window)
+    forward.check_status(q.device)
+    assert oatt.relative_l2(f32(out), oracle_full(q, k, v, window=window)) < ORACLE_TOL
+
+
+def test_batched_fp16_with_ragged_tail_and_batch_isolation():
+    """[B,S,H,128] FP16 with S not a multiple of 128; a zero batch item gives zero output
+    (tests/gpu/test_attention.py:42-53 of the reference)."""
+    ovc, api, forward = _api()
+    g = torch.Generator(device=DEV).manual_seed(9)
+    q, k, v = [torch.randn(3, 1000, 3, 128, generator=g, device=DEV).to(torch.float16) for _ in range(3)]
+    v[1] = 0
+    out = ovc.attention(q, k, v)
+    forward.check_status(q.device)
+    assert out.shape == q.shape and out.dtype == torch.bfloat16
+    assert not out[1].any()
+    assert oatt.relative_l2(f32(out), oracle_full(q, k, v)) < ORACLE_TOL
+    single = ovc.attention(q[2], k[2], v[2])
+    assert torch.equal(single, out[2])
+    assert torch.equal(ovc.attention(q[2:3], k[2:3], v[2:3])[0], single)  # 4-D with B == 1
+
+
+def test_headline_batched_shape_sampled_rows():
+    """General path at [4,8191,24,128] FP16: sampled (batch, head, 256-row block)s against the oracle."""
+    ovc, api, forward = _api()
+    g = torch.Generator(device=DEV).manual_seed(4)
+    q, k, v = [torch.randn(4, 8191, 24, 128, generator=g, device=DEV).to(torch.float16) for _ in range(3)]
+    out = ovc.attention(q, k, v)
+    forward.check_status(q.device)
+    prepared = api.prepare_fp8(q, k, v)
+    for b, head, m in ((0, 0, 0), (3, 23, 31), (1, 11, 17)):
+        sub = type("P", (), dict(q=prepared.q[b], k=prepared.k[b], v=prepared.v[b], q_descale=prepared.q_descale[b : b + 1],
+                                 k_descale=prepared.k_descale[b : b + 1], v_descale=prepared.v_descale[b : b + 1],
+                                 v_prepacked=False))
+        rows, expect = oracle_rows(sub, [m], [head])
+        assert oatt.relative_l2(f32(out[b, :, head])[rows], expect[:, 0]) < ORACLE_TOL
+    assert torch.isfinite(out.float()).all()
+
+
+def test_cross_attention_and_scale():
+    ovc, api, forward = _api()
+    g = torch.Generator(device=DEV).manual_seed(21)
+    q = torch.randn(300, 2, 128, generator=g, device=DEV).to(torch.bfloat16)
+    k, v = [torch.randn(777, 2, 128, generator=g, device=DEV).to(torch.bfloat16) for _ in range(2)]
+    out = ovc.attention(q, k, v, softmax_scale=0.05)
+    forward.check_status(q.device)
+    qf, kf, vf = (f32(t)[None] for t in (q, k, v))
+    pq, pk, pv = oprep.quantize_per_block(qf), oprep.quantize_per_block(kf), oprep.quantize_per_head(vf)
+    expect = oatt.expcast_attention(pq[0][0], pk[0][0], pv[0][0], pq[1][0], pk[1][0], pv[1][0], softmax_scale=0.05)
+    assert oatt.relative_l2(f32(out), expect) < ORACLE_TOL
+    assert oatt.relative_l2(f32(out), oatt.exact_attention(qf[0], kf[0], vf[0], softmax_scale=0.05)) < 0.10
+
+
+def test_validation_errors():
+    ovc, api, forward = _api()
+    q = torch.randn(64, 2, 128, device=DEV, dtype=torch.bfloat16)
+    with pytest.raises(ValueError, match="matching dtypes"):
+        ovc.attention(q, q, q.float())
+    with pytest.raises(ValueError, match="detach"):
+        ovc.attention(q.clone().requires_grad_(), q, q)
+    with pytest.raises(NotImplementedError, match="causal"):
+        ovc.attention(q, q, q, causal=True)
+    with pytest.raises(NotImplementedError, match="return_lse"):
+        ovc.attention(q, q, q, return_lse=True)
+    with pytest.raises(ValueError, match="not available"):
+        ovc.attention(q, q, q, mode="bf16", version="reference")
+    prepared = api.prepare_fp8(q, q, q)
+    with pytest.raises(ValueError, match="requires version"):
+        api.attention_fp8(prepared, version="reference")
+
+
+def test_cuda_graph_replay_reads_current_inputs():
+    # tests/gpu/test_attention.py:90-107 of the reference
+    ovc, api, forward = _api()
+    torch.manual_seed(3)
+    q, k, v = [torch.randn(513, 2, 128, device=DEV, dtype=torch.bfloat16) for _ in range(3)]
+    ovc.attention(q, k, v)  # warm up allocator and status word outside capture
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        out = ovc.attention(q, k, v)
+    graph.replay()
+    torch.cuda.synchronize()
+    first = out.clone()
+    assert torch.equal(first, ovc.attention(q, k, v))
+    v.mul_(2)
+    graph.replay()
+    torch.cuda.synchronize()
+    forward.check_status(q.device)
+    assert torch.equal(out, ovc.attention(q, k, v))
+    assert not torch.equal(out, first)
+
+
+@pytest.mark.parametrize("s,h", [(32768, 8), (73397, 7)])
+def test_packed_path_full_size(s, h):
+    """Packed fast path at the benchmark sizes: sampled 256-row blocks against the oracle, fused versus
+    general preparation bitwise, and exact doubling when V doubles (a power-of-two scale)."""
+    ovc, api, forward = _api()
+    q, k, v = structured_qkv(s, h, seed=s + h) if s > 40000 else [
+        torch.randn(s, h, 128, device=DEV, dtype=torch.bfloat16, generator=torch.Generator(device=DEV).manual_seed(s))
+        for _ in range(3)]
+    fused = api.prepare_fp8_fused(q, k, v)
+    out = api.attention_fp8(fused)
+    forward.check_status(q.device)
+    assert torch.equal(out, ovc.attention(q, k, v))
+    assert torch.equal(out, ovc.attention(q, k, v, preparation="fused"))
+    assert torch.equal(out, ovc.attention(q[None], k[None], v[None])[0])
+    assert torch.equal(out, api.attention_fp8(api.prepare_fp8(q, k, v)))  # general preparation, packed in the call
+    assert torch.equal(out, ovc.attention(q, k, v, preparation="unfused"))
+    m_blocks = (s + 255) // 256
+    for head, m in ((0, 0), (h - 1, m_blocks - 1), (h // 2, m_blocks // 2)):
+        rows, expect = oracle_rows(fused, [m], [head])
+        got = f32(out[:, head])[rows]
+        assert oatt.relative_l2(got, expect[:, 0]) < ORACLE_TOL
+        pick = rows[:: max(1, len(rows) // 16)]
+        exact = oatt.exact_attention(f32(q[pick][:, head : head + 1]), f32(k[:, head : head + 1]), f32(v[:, head : head + 1]))
+        assert oatt.relative_l2(f32(out[pick][:, head : head + 1]), exact) < 0.10
+    doubled = ovc.attention(q, k, v * 2)
+    assert torch.equal(doubled.float(), out.float() * 2)
+    assert torch.isfinite(out.float()).all()
+
+
+def test_prepacked_contract_errors():
+    # tests/gpu/test_preparation.py:106-125 of the reference
+    import dataclasses
+
+    ovc, api, forward = _api()
+    q = torch.randn(32768, 1, 128, device=DEV, dtype=torch.bfloat16)
+    fused = api.prepare_fp8_fused(q, q, q)
+    with pytest.raises(ValueError, match="Prepacked V"):
+        api.attention_fp8(fused, causal=True)
+    broken = dataclasses.replace(fused, v=fused.v.contiguous())
+    with pytest.raises(ValueError, match="v_prepacked"):
+        api.attention_fp8(broken)

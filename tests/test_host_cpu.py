@@ -1,0 +1,159 @@
+"""Host-side mirror of the reference API: lazy import, argument policy, sharding arithmetic."""
+
+import os
+import subprocess
+import sys
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+PACKAGE_ROOT = os.path.join(ROOT, "open-vc-attention_b200")
+
+
+def test_import_needs_neither_torch_nor_cuda():
+    # tests/cpu/test_contracts.py:85-96 of the reference
+    code = (
+        "import sys; sys.path.insert(0, %r); import open_vc_attn; "
+        "assert 'torch' not in sys.modules and 'ctypes' not in sys.modules; "
+        "print(sorted(open_vc_attn.__all__))" % PACKAGE_ROOT
+    )
+    out = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, check=True).stdout
+    for name in ("attention", "attention_fp8", "prepare_fp8", "prepare_fp8_fused", "prepare_v_repair",
+                 "attention_v_repair", "raw_forward"):
+        assert name in out
+
+
+def test_defaults_match_the_reference():
+    from open_vc_attn import _dispatch
+
+    assert _dispatch.DEFAULT_VERSION == "open-vc"
+    assert _dispatch.DEFAULT_MID_WINDOW_BLOCKS == 4
+    with pytest.raises(ValueError, match="not available"):
+        _dispatch.require_version("reference")
+    with pytest.raises(ValueError, match="Unknown implementation"):
+        _dispatch.require_version("other")
+
+
+def test_cpu_tensors_are_refused_with_the_reference_messages():
+    torch = pytest.importorskip("torch")
+    import open_vc_attn
+    from open_vc_attn import api
+
+    q = torch.zeros(4, 2, 128, dtype=torch.bfloat16)
+    with pytest.raises(ValueError, match="same CUDA device"):
+        open_vc_attn.attention(q, q, q)
+    with pytest.raises(ValueError, match=r"\[S,H,128\] or \[B,S,H,128\]"):
+        api.validate_qkv(q[0], q[0], q[0])
+    with pytest.raises(ValueError, match="D=128"):
+        api.validate_qkv(q[..., :64], q[..., :64], q[..., :64])
+    with pytest.raises(ValueError, match="matching K/V shapes"):
+        api.validate_qkv(q, q, q[:2])
+
+
+def test_argument_policy_of_attention(monkeypatch):
+    """Mode/version/preparation checks come before any device work (src/open_vc_attn/api.py:198-211)."""
+    torch = pytest.importorskip("torch")
+    from open_vc_attn import api
+
+    monkeypatch.setattr(api, "validate_qkv", lambda *a, **k: None)
+    monkeypatch.setattr(api, "_fused_preparation_eligible", lambda *a, **k: False)
+    q = torch.zeros(4, 2, 128, dtype=torch.bfloat16)
+    with pytest.raises(ValueError, match="mode must be bf16 or expcast"):
+        api.attention(q, q, q, mode="fp4")
+    with pytest.raises(ValueError, match='requires version="reference"'):
+        api.attention(q, q, q, mode="bf16")
+    with pytest.raises(ValueError, match="not available"):
+        api.attention(q, q, q, mode="bf16", version="reference")
+    with pytest.raises(ValueError, match="preparation must be"):
+        api.attention(q, q, q, preparation="maybe")
+    with pytest.raises(ValueError, match="Fused preparation requires"):
+        api.attention(q, q, q, preparation="fused")
+    with pytest.raises(ValueError, match="requires version"):
+        api.attention_fp8(object(), version="reference")
+
+
+def test_unbuilt_options_raise_instead_of_degrading():
+    torch = pytest.importorskip("torch")
+    from open_vc_attn import baselines, forward
+
+    q = torch.zeros(4, 2, 128, dtype=torch.float8_e4m3fn)
+    d3 = torch.ones(1, 2, 1)
+    d2 = torch.ones(1, 2)
+    common = dict(q_descale=d3, k_descale=d3, v_descale=d2, expcast=True)
+    with pytest.raises(NotImplementedError, match="causal"):
+        forward.flash_attn_fwd(q, q, q, causal=True, **common)
+    with pytest.raises(NotImplementedError, match="return_lse"):
+        forward.flash_attn_fwd(q, q, q, return_lse=True, **common)
+    with pytest.raises(NotImplementedError, match="Unsupported kernel options"):
+        forward.flash_attn_fwd(q, q, q, v_smooth=True, **common)
+    with pytest.raises(ValueError, match="v_prepacked must use"):
+        forward.flash_attn_fwd(q, q, q, v_prepacked=True, **common)
+    with pytest.raises(ValueError, match="positive finite softmax_scale"):
+        forward.flash_attn_fwd(q, q, q, softmax_scale=0.0, **common)
+    with pytest.raises(NotImplementedError):
+        baselines.vc_attention(q, q, q)
+
+
+def test_repair_budget_validation(monkeypatch):
+    # tests/gpu/test_v_repair.py:84-88 of the reference
+    torch = pytest.importorskip("torch")
+    from open_vc_attn import v_repair
+
+    monkeypatch.setattr(v_repair, "validate_qkv", lambda *a, **k: None)
+    q = torch.zeros(40000, 1, 128, dtype=torch.bfloat16)
+    for bad in (-0.1, 1.0, float("nan"), float("inf")):
+        with pytest.raises(ValueError, match="budget"):
+            v_repair.prepare_v_repair(q, q, q, budget=bad)
+    with pytest.raises(ValueError, match="S >= 32768"):
+        v_repair.prepare_v_repair(q[:100], q[:100], q[:100], budget=0.1)
+
+
+def test_head_ranges_cover_all_heads_once():
+    from open_vc_attn.sharding import head_range
+
+    for heads, world in ((56, 8), (56, 4), (14, 4), (14, 8), (7, 8), (1, 2), (5, 3)):
+        ranges = [head_range(heads, world, r) for r in range(world)]
+        assert ranges[0][0] == 0 and ranges[-1][1] == heads
+        assert all(a[1] == b[0] for a, b in zip(ranges, ranges[1:]))
+        sizes = [b - a for a, b in ranges]
+        assert max(sizes) - min(sizes) <= 1
+    assert head_range(56, 8, 3) == (21, 28)
+    assert head_range(7, 8, 7) == (7, 7)  # one idle rank
+    with pytest.raises(ValueError):
+        head_range(8, 2, 2)
+
+
+def _gather_worker(rank, world, port, heads, result):
+    import torch
+    import torch.distributed as dist
+
+    from open_vc_attn.sharding import gather_heads, head_range
+
+    dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world)
+    try:
+        h0, h1 = head_range(heads, world, rank)
+        full = torch.arange(3 * heads * 128, dtype=torch.float32).reshape(3, heads, 128).to(torch.bfloat16)
+        merged = gather_heads(full[:, h0:h1].contiguous(), heads)
+        result[rank] = bool(torch.equal(merged, full))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("heads", [4, 5])
+def test_gather_heads_with_two_gloo_ranks(heads):
+    """World size 2 on CPU: uneven head counts are padded for the all-gather and trimmed after it."""
+    pytest.importorskip("torch")
+    import torch.multiprocessing as mp
+
+    sys.path.insert(0, PACKAGE_ROOT)
+    port = 29500 + (os.getpid() % 2000) + heads
+    manager = mp.Manager()
+    result = manager.dict()
+    ctx = mp.get_context("spawn")
+    procs = [ctx.Process(target=_gather_worker, args=(r, 2, port, heads, result)) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(120)
+        assert p.exitcode == 0
+    assert result[0] and result[1]
