@@ -459,6 +459,13 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
             uint32_t codes[32];
 #pragma unroll
             for (int c = 0; c < 32; ++c) codes[c] = encode4(s[4 * c], s[4 * c + 1], s[4 * c + 2], s[4 * c + 3], scale2, bias2);
+            if (it > 0) {
+                // The stage's previous PV (step it-1) is issued after this step's QK, so the score
+                // barrier does not cover it: wait for it before P is overwritten or O is rescaled.
+                ok = __all_sync(0xFFFFFFFFu, wait_bar(sm, &sm.pv_done[stage], (it - 1) & 1, p.status));
+                if (!ok) break;
+                tc_fence_after();
+            }
             tmem_st32(t_p, codes);
             if ((warp & 3) == 0) OVC_TL(it, stage * 6 + 4);
 #ifdef OVC_DEBUG_DUMP
@@ -470,12 +477,6 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
 
             const bool first_repair = p.first_tile > 0 && j == p.first_tile - 1;
             const bool rescale = it > 0 && __any_sync(0xFFFFFFFFu, alpha < 1.0f);
-            if (first_repair || rescale) {
-                // Both touch this stage's accumulator: its previous PV (step it-1) must have landed.
-                ok = __all_sync(0xFFFFFFFFu, wait_bar(sm, &sm.pv_done[stage], (it - 1) & 1, p.status));
-                if (!ok) break;
-                tc_fence_after();
-            }
             if (first_repair) {
                 // First repair tile: the denominator holds the original tokens' total only.
                 saved_denominator = __uint_as_float(tmem_ld1(t_o + kDim));

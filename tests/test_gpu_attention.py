@@ -158,9 +158,11 @@ def test_packed_path_full_size(s, h):
     """Packed fast path at the benchmark sizes: sampled 256-row blocks against the oracle, fused versus
     general preparation bitwise, and exact doubling when V doubles (a power-of-two scale)."""
     ovc, api, forward = _api()
-    q, k, v = structured_qkv(s, h, seed=s + h) if s > 40000 else [
-        torch.randn(s, h, 128, device=DEV, dtype=torch.bfloat16, generator=torch.Generator(device=DEV).manual_seed(s))
-        for _ in range(3)]
+    if s > 40000:
+        q, k, v = structured_qkv(s, h, seed=s + h)
+    else:
+        g = torch.Generator(device=DEV).manual_seed(s)
+        q, k, v = [torch.randn(s, h, 128, device=DEV, generator=g).to(torch.bfloat16) for _ in range(3)]
     fused = api.prepare_fp8_fused(q, k, v)
     out = api.attention_fp8(fused)
     forward.check_status(q.device)
