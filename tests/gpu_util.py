@@ -26,20 +26,10 @@ def packed_buffer(view):
 
 
 def structured_qkv(s, h, seed, dtype=torch.bfloat16, device=DEV):
-    """Synthetic stand-in for the video-DiT captures: Q,K ~ N(0,1) with 4 of 128 channels per head
-    scaled x8 and a LogNormal(0,0.3) per-token norm; V ~ N(mu_h,1) with per-head channel means
-    mu_h ~ N(0,2)."""
-    g = torch.Generator(device=device).manual_seed(seed)
-    q = torch.randn(s, h, 128, generator=g, device=device)
-    k = torch.randn(s, h, 128, generator=g, device=device)
-    for t in (q, k):
-        for head in range(h):
-            idx = torch.randperm(128, generator=g, device=device)[:4]
-            t[:, head, idx] *= 8
-        t *= torch.exp(0.3 * torch.randn(s, 1, 1, generator=g, device=device))
-    mu = 2.0 * torch.randn(1, h, 128, generator=g, device=device)
-    v = torch.randn(s, h, 128, generator=g, device=device) + mu
-    return q.to(dtype), k.to(dtype), v.to(dtype)
+    """Synthetic stand-in for the video-DiT captures (see open_vc_attn/synthetic.py)."""
+    from open_vc_attn.synthetic import video_dit_qkv
+
+    return video_dit_qkv(s, h, seed=seed, dtype=dtype, device=device)
 
 
 def oracle_rows(prepared, m_blocks, heads, window=4, repair_kd=None):
