@@ -9,8 +9,9 @@
  *
  * Conventions
  *   - Every pointer is a DEVICE pointer unless stated otherwise; the caller owns
- *     all memory.  No entry point allocates, frees or synchronises, so all of
- *     them may be captured in a CUDA graph (the one exception is marked).
+ *     all memory.  No entry point allocates, frees or synchronises.  The entry
+ *     points that replace a stage of the reference stay capturable in a CUDA
+ *     graph, as that stage is (tested through the Python layer).
  *   - Work is enqueued on `stream` (a cudaStream_t passed as void*) of the
  *     device that is current in the calling thread.
  *   - `dtype`: OVC_F16 or OVC_BF16, the element type of the 16-bit inputs.
@@ -37,6 +38,7 @@ extern "C" {
 #define OVC_ERR_CUDA (-2)        /* a CUDA runtime call failed; see ovc_last_cuda_error() */
 #define OVC_ERR_DRIVER (-3)      /* tensor-map creation failed */
 #define OVC_ERR_UNSUPPORTED (-4) /* device is not sm_100 */
+#define OVC_ERR_TOO_LARGE (-5)   /* a size exceeds what the library's built-in scratch memory can hold */
 
 /* Bits of the device status word written by ovc_attention (0 = clean run). */
 #define OVC_STATUS_WAIT_EXPIRED 1u /* a bounded barrier wait gave up; the output is invalid */
@@ -87,6 +89,29 @@ int ovc_quantize_per_head(const void* v, int dtype, int64_t B, int64_t S, int64_
 int ovc_prepare_fused(const void* q, const void* k, const void* v, int dtype, int64_t S, int64_t H,
                       void* q8, void* k8, void* v_packed, float* q_descale, float* k_descale,
                       float* v_descale, float* amax_ws, void* stream);
+
+/*
+ * ovc_prepare_fused without the caller-provided scratch buffer.  (No counterpart in the reference; it
+ * exists for this library's callers only.)
+ *
+ * Some hosts of this code cannot hand over even a few bytes of extra device memory per call: an
+ * inference server whose memory pool was sized up front and already owns the whole GPU, a plugin that
+ * is given input and output buffers and nothing else, or any caller that must not reach cudaMalloc on
+ * its hot path.  For them the per-head max |v| scratch lives inside the library, in a fixed array of
+ * OVC_STATIC_MAX_HEADS (4096) floats that every GPU loading libovc.so holds until the process ends.
+ * The call allocates and frees nothing, on the device or through any library.
+ *
+ *   - H > 4096 is refused with OVC_ERR_TOO_LARGE; all other arguments as for ovc_prepare_fused.
+ *   - The first call on each device looks up the array's device address (with that device current).
+ *     Make that first call ahead of any stream capture.
+ *   - All calls on a device share the one array.  Each call resets the entries it uses before
+ *     accumulating, so back-to-back calls on one stream are independent; calls whose kernels overlap
+ *     on the GPU (different streams, no ordering) race on it and must not be issued.
+ *   - Results are bit-identical to ovc_prepare_fused.
+ */
+int ovc_prepare_fused_static(const void* q, const void* k, const void* v, int dtype, int64_t S, int64_t H,
+                             void* q8, void* k8, void* v_packed, float* q_descale, float* k_descale,
+                             float* v_descale, void* stream);
 
 /*
  * FP8 byte transpose into the packed V layout.  Replaces transpose_v / pack_v

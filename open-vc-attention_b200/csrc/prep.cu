@@ -377,6 +377,43 @@ bool bad_dims(int64_t B, int64_t S, int64_t H) {
 
 using namespace ovc;
 
+// ---- scratch that lives inside the library (used only by ovc_prepare_fused_static) --------------
+//
+// One float per head for the per-head max |v|.  Every GPU that loads the library holds these 16 KB
+// until the process exits.  In host code the array's name is only a handle for the runtime: the
+// device address has to be asked for, once per device, with that device current.
+#define OVC_STATIC_MAX_HEADS 4096
+static __device__ __align__(256) float g_static_amax[OVC_STATIC_MAX_HEADS];
+
+namespace {
+
+constexpr int kMaxDevices = 64;
+float* g_static_amax_ptr[kMaxDevices] = {};
+
+// Device address of g_static_amax on the current device (looked up on the first call per device).
+int static_amax_pointer(float** out) {
+    int device = 0;
+    cudaError_t err = cudaGetDevice(&device);
+    if (err != cudaSuccess) {
+        set_last_cuda_error(err);
+        return OVC_ERR_CUDA;
+    }
+    if (device < 0 || device >= kMaxDevices) return OVC_ERR_ARGUMENT;
+    if (g_static_amax_ptr[device] == nullptr) {
+        float* ptr = nullptr;
+        err = cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_static_amax);
+        if (err != cudaSuccess || ptr == nullptr) {
+            set_last_cuda_error(err);
+            return OVC_ERR_CUDA;
+        }
+        g_static_amax_ptr[device] = ptr;
+    }
+    *out = g_static_amax_ptr[device];
+    return OVC_OK;
+}
+
+}  // namespace
+
 extern "C" {
 
 int ovc_version(void) { return 1; }
@@ -388,6 +425,7 @@ const char* ovc_error_string(int code) {
         case OVC_ERR_CUDA: return "CUDA runtime error (see ovc_last_cuda_error)";
         case OVC_ERR_DRIVER: return "tensor-map creation failed (see ovc_last_cuda_error)";
         case OVC_ERR_UNSUPPORTED: return "device is not sm_100";
+        case OVC_ERR_TOO_LARGE: return "size exceeds the capacity of the library's built-in scratch memory";
         default: return "unknown error";
     }
 }
@@ -507,5 +545,18 @@ int ovc_repair_rows(void* k_all, void* v_all, const void* v_src, int dtype, cons
         repair_rows_kernel<OVC_F16><<<grid, 32, 0, s>>>(ka, va, v_src, k_descale, v_descale, index, repair_kd, selected, rows, S, static_cast<int>(H), k_blocks);
     return check_launch();
 }
+
+int ovc_prepare_fused_static(const void* q, const void* k, const void* v, int dtype, int64_t S, int64_t H, void* q8,
+                             void* k8, void* v_packed, float* q_descale, float* k_descale, float* v_descale,
+                             void* stream) {
+    if (H > OVC_STATIC_MAX_HEADS) return OVC_ERR_TOO_LARGE;
+    float* scratch = nullptr;
+    const int rc = static_amax_pointer(&scratch);
+    if (rc != OVC_OK) return rc;
+    // The first preparation kernel resets scratch[0..H) before the amax pass accumulates into it,
+    // so nothing is carried over from the previous call.
+    return ovc_prepare_fused(q, k, v, dtype, S, H, q8, k8, v_packed, q_descale, k_descale, v_descale, scratch, stream);
+}
+
 
 }  // extern "C"
