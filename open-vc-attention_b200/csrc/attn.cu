@@ -14,14 +14,15 @@
 //
 // Schedule.  Issuing an MMA group blocks the issuing thread for about as long as the group runs,
 // and every barrier wait and tcgen05.commit in that thread costs tensor-pipe idle time, so the MMA
-// warp is given the fewest possible of both.  Per key step n it issues two groups,
-//     gate0 -> S = Q0 K(n)^T, commit, O0 += P0(n-1) [V(n-1) | 1], commit
-//     gate1 -> S = Q1 K(n)^T, commit, O1 += P1(n-1) [V(n-1) | 1], commit
-// where gate0 collects "P0(n-1) stored" from stage 0, "S1(n-1) copied out" from stage 1 and
-// "V(n-1), K(n) landed" from the relay, and gate1 collects "S0(n) copied out" and "P1(n-1) stored".
-// QK is issued before the PV of the same stage so that the next scores are ready when the
-// conversion warps come back.  Shared-memory slots are recycled from progress counters that the
-// conversion warps publish, not from extra commits.
+// warp is given the fewest possible of both: one gate per stage and key step.  A conversion thread
+// of stage s arrives on gate[s] once per step, right after it has copied its scores S_s(n) out of
+// tensor memory; by then it has also stored P_s(n-1).  On gate[s] the MMA warp issues
+//     S = Q_{1-s} K^T for the other stage's next step   (the score buffer is free again), commit
+//     O_s += P_s(n-1) [V(n-1) | 1], commit
+// so the other stage's scores are produced while this stage converts, and a stage finds its next
+// scores waiting when it comes back.  The relay adds "K / V tile landed" to the same gates.
+// Shared-memory slots are recycled from progress counters that the conversion warps publish, not
+// from extra commits.
 //
 // Tensor memory map (512 columns): S 0..127 (shared by both stages), P0 128..159, P1 160..191,
 // O0 192..327, O1 328..463; each O region is 128 output columns followed by 8 copies of the
@@ -33,6 +34,13 @@
 
 #include "common.cuh"
 #include "sm100_ptx.cuh"
+
+#ifndef OVC_ENCODE_SCALAR
+#define OVC_ENCODE_SCALAR 0
+#endif
+#ifndef OVC_MAX3
+#define OVC_MAX3 0
+#endif
 
 namespace ovc {
 namespace {
@@ -62,7 +70,7 @@ struct SmemLayout {
     uint64_t o_full[2], drain;
     uint32_t tmem_base;
     volatile uint32_t abort_flag;
-    volatile int progress[2];  // progress[s] = number of s_full[s] phases observed by stage s
+    volatile int progress[3];  // [0],[1]: s_full phases seen by stage 0 / 1; [2]: PV steps of stage 1 seen done
 };
 
 struct AttnParams {
@@ -165,19 +173,77 @@ __device__ __forceinline__ uint64_t pack2(float a, float b) {
     return r;
 }
 
-// Four scores -> four ExpCast E4M3 codes: y = x*scale + bias (units of 2^-24), rounded to an FP16
-// subnormal whose low byte is the integer code; ReLU supplies the clamp at zero.
-__device__ __forceinline__ uint32_t encode4(uint32_t x0, uint32_t x1, uint32_t x2, uint32_t x3, uint64_t scale2,
-                                            uint64_t bias2) {
-    uint32_t out;
-    asm("{\n\t.reg .b64 xp, r;\n\t.reg .f32 f0, f1, f2, f3;\n\t.reg .b32 lo, hi;\n\t"
-        "mov.b64 xp, {%1, %2};\n\tfma.rn.f32x2 r, xp, %5, %6;\n\tmov.b64 {f0, f1}, r;\n\t"
-        "mov.b64 xp, {%3, %4};\n\tfma.rn.f32x2 r, xp, %5, %6;\n\tmov.b64 {f2, f3}, r;\n\t"
-        "cvt.rn.relu.f16x2.f32 lo, f1, f0;\n\tcvt.rn.relu.f16x2.f32 hi, f3, f2;\n\t"
-        "prmt.b32 %0, lo, hi, 0x6420;\n\t}"
-        : "=r"(out)
-        : "r"(x0), "r"(x1), "r"(x2), "r"(x3), "l"(scale2), "l"(bias2));
-    return out;
+// ExpCast codes of 128 scores: y = x*scale + bias in units of 2^-24 (one packed FMA per pair), rounded
+// to an FP16 subnormal whose low byte is the integer code (ReLU supplies the clamp at zero), low bytes
+// gathered four at a time.  Written stage by stage over 32 columns so that every stage is a run of
+// independent instructions.
+__device__ __forceinline__ uint64_t ffma2(uint64_t a, uint64_t b, uint64_t c) {
+    uint64_t d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+__device__ __forceinline__ uint64_t pack_u2(uint32_t lo, uint32_t hi) {
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "r"(lo), "r"(hi));
+    return r;
+}
+__device__ __forceinline__ uint32_t half_codes(uint64_t y) {
+    uint32_t lo, hi, h;
+    asm("mov.b64 {%0, %1}, %2;" : "=r"(lo), "=r"(hi) : "l"(y));
+    asm("cvt.rn.relu.f16x2.f32 %0, %1, %2;" : "=r"(h) : "f"(__uint_as_float(hi)), "f"(__uint_as_float(lo)));
+    return h;
+}
+__device__ __forceinline__ void encode128(const uint32_t (&s)[128], uint64_t scale2, uint64_t bias2, uint32_t (&codes)[32]) {
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+        uint32_t h[16];
+#if OVC_ENCODE_SCALAR
+        float sc, bi, dummy;
+        asm("mov.b64 {%0, %1}, %2;" : "=f"(sc), "=f"(dummy) : "l"(scale2));
+        asm("mov.b64 {%0, %1}, %2;" : "=f"(bi), "=f"(dummy) : "l"(bias2));
+        float y[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) y[i] = fmaf(__uint_as_float(s[32 * c + i]), sc, bi);
+#pragma unroll
+        for (int i = 0; i < 16; ++i)
+            asm("cvt.rn.relu.f16x2.f32 %0, %1, %2;" : "=r"(h[i]) : "f"(y[2 * i + 1]), "f"(y[2 * i]));
+#else
+        uint64_t y[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) y[i] = ffma2(pack_u2(s[32 * c + 2 * i], s[32 * c + 2 * i + 1]), scale2, bias2);
+#pragma unroll
+        for (int i = 0; i < 16; ++i) h[i] = half_codes(y[i]);
+#endif
+#pragma unroll
+        for (int i = 0; i < 8; ++i) codes[8 * c + i] = __byte_perm(h[2 * i], h[2 * i + 1], 0x6420);
+    }
+}
+
+// Row max of 128 scores by a level-wise tree of two-input max (full-rate pipe).
+__device__ __forceinline__ float max128(const uint32_t (&s)[128]) {
+#if OVC_MAX3
+    float m9[43];
+#pragma unroll
+    for (int c = 0; c < 42; ++c)
+        m9[c] = fmax3(__uint_as_float(s[3 * c]), __uint_as_float(s[3 * c + 1]), __uint_as_float(s[3 * c + 2]));
+    m9[42] = fmaxf(__uint_as_float(s[126]), __uint_as_float(s[127]));
+    float m3[15];
+#pragma unroll
+    for (int c = 0; c < 14; ++c) m3[c] = fmax3(m9[3 * c], m9[3 * c + 1], m9[3 * c + 2]);
+    m3[14] = m9[42];
+    float m1[5];
+#pragma unroll
+    for (int c = 0; c < 5; ++c) m1[c] = fmax3(m3[3 * c], m3[3 * c + 1], m3[3 * c + 2]);
+    return fmaxf(fmax3(m1[0], m1[1], m1[2]), fmaxf(m1[3], m1[4]));
+#endif
+    float m[64];
+#pragma unroll
+    for (int i = 0; i < 64; ++i) m[i] = fmaxf(__uint_as_float(s[i]), __uint_as_float(s[i + 64]));
+#pragma unroll
+    for (int w = 32; w > 0; w >>= 1)
+#pragma unroll
+        for (int i = 0; i < w; ++i) m[i] = fmaxf(m[i], m[i + w]);
+    return m[0];
 }
 
 __device__ __forceinline__ uint32_t bf16x2(float lo, float hi) {
@@ -220,12 +286,13 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         }
         for (int i = 0; i < kKStages; ++i) mbar_init(smem_addr(&sm.k_full[i]), 1);
         for (int i = 0; i < kVStages; ++i) mbar_init(smem_addr(&sm.v_full[i]), 1);
-        mbar_init(smem_addr(&sm.gate[0]), 257);  // 128 + 128 conversion threads + the relay
-        mbar_init(smem_addr(&sm.gate[1]), 256);
+        mbar_init(smem_addr(&sm.gate[0]), 129);  // 128 conversion threads of the stage + the relay
+        mbar_init(smem_addr(&sm.gate[1]), 129);
         mbar_init(smem_addr(&sm.drain), 1);
         sm.abort_flag = 0;
         sm.progress[0] = 0;
         sm.progress[1] = 0;
+        sm.progress[2] = 0;
         mbar_init_fence();
     }
     // Rows 128.. of every V slot: E4M3 1.0, so PV also accumulates the row sums of P.
@@ -266,9 +333,8 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
                     mbar_expect_tx(smem_addr(&sm.k_full[ks]), kTileBytes);
                     tma_load_4d(smem_addr(sm.k[ks]), &tmap_k, smem_addr(&sm.k_full[ks]), 0, head, j * kTile, batch, keep);
                     issued_k = it + 1;
-                    // V(it - kVStages) was last read by stage 1's PV, which the commit after stage 0's
-                    // QK two steps later covers.
-                    if (!wait_progress(sm, 0, it - kVStages + 3, p.status)) break;
+                    // V(it - kVStages) was last read by stage 1's PV of that step.
+                    if (!wait_progress(sm, 2, it - kVStages + 1, p.status)) break;
                     mbar_expect_tx(smem_addr(&sm.v_full[vs]), kTileBytes);
                     tma_load_4d(smem_addr(sm.v[vs]), &tmap_v, smem_addr(&sm.v_full[vs]), j * kTile, 0, head, batch, keep);
                     issued_v = it + 1;
@@ -301,65 +367,53 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
             bool ok = wait_bar(sm, &sm.q_full[0], 0, p.status) && wait_bar(sm, &sm.q_full[1], 0, p.status) &&
                       wait_bar(sm, &sm.k_full[0], 0, p.status);
             ok = __all_sync(0xFFFFFFFFu, ok);
-            // Step n: stage s gets S = Q[s] K(n)^T and then O[s] += P[s](n-1) [V(n-1) | 1].
+            if (ok) {
+                mma4_f8_ss(tmem + kColS, smem_desc_lo(smem_addr(sm.q[0])), smem_desc_lo(smem_addr(sm.k[0])), idesc_qk);
+                mma_commit_elect(smem_addr(&sm.s_full[0]));
+            }
+            // gate[s] completion n: stage s has copied S_s(n) out (n < N) and stored P_s(n-1) (n > 0).
+            // Then: scores of the other stage's next step (stage 1: step n, stage 0: step n+1), PV_s(n-1).
             for (int n = 0; ok && n <= n_iters; ++n) {
                 const int it = n;
-                const uint64_t kdesc = smem_desc_sw128(smem_addr(sm.k[n % kKStages]));
-                const uint64_t vdesc = smem_desc_sw128(smem_addr(sm.v[(n + kVStages - 1) % kVStages]));
                 for (int s = 0; s < 2; ++s) {
-                    if (n > 0 || s == 1) {
-                        // gate[0] completion n-1 / gate[1] completion n
-                        OVC_TL(it, 12 + s * 6 + 0);
-                        ok = __all_sync(0xFFFFFFFFu, wait_bar(sm, &sm.gate[s], (n - 1 + s) & 1, p.status));
-                        if (!ok) break;
-                        tc_fence_after();
-                        OVC_TL(it, 12 + s * 6 + 1);
+                    OVC_TL(it, 12 + s * 6 + 0);
+                    ok = __all_sync(0xFFFFFFFFu, wait_bar(sm, &sm.gate[s], n & 1, p.status));
+                    if (!ok) break;
+                    tc_fence_after();
+                    OVC_TL(it, 12 + s * 6 + 1);
+                    const int qk_step = n + s;  // s = 0 feeds stage 1 step n; s = 1 feeds stage 0 step n + 1
+                    if (qk_step < n_iters) {
+                        mma4_f8_ss(tmem + kColS, smem_desc_lo(smem_addr(sm.q[1 - s])),
+                                   smem_desc_lo(smem_addr(sm.k[qk_step % kKStages])), idesc_qk);
+                        mma_commit_elect(smem_addr(&sm.s_full[1 - s]));
                     }
-                    if (lane == 0) {
-                        if (n < n_iters) {
-                            const uint64_t a = smem_desc_sw128(smem_addr(sm.q[s]));
-#pragma unroll
-                            for (int kk = 0; kk < 4; ++kk) {
-                                mma_f8_ss(tmem + kColS, a + 2 * kk, kdesc + 2 * kk, idesc_qk, kk > 0 ? 1u : 0u);
-                                if (s == 0) OVC_TL(it, 24 + kk);
-                            }
-                            mma_commit(smem_addr(&sm.s_full[s]));
-                            if (s == 0) OVC_TL(it, 28);
-                        }
-                        if (n > 0) {
-                            const uint32_t d = tmem + kColO + s * kColOStride, a = tmem + kColP + 32 * s;
-#pragma unroll
-                            for (int kk = 0; kk < 4; ++kk) {
-                                mma_f8_ts(d, a + 8 * kk, vdesc + 2 * kk, idesc_pv, (n > 1 || kk > 0) ? 1u : 0u);
-                                if (s == 0 && kk == 1) OVC_TL(it, 29);
-                                if (s == 0 && kk == 3) OVC_TL(it, 30);
-                            }
-                            mma_commit(smem_addr(n < n_iters ? &sm.pv_done[s] : &sm.o_full[s]));
-                            if (s == 0) OVC_TL(it, 31);
-                        }
+                    if (n > 0) {
+                        mma4_f8_ts(tmem + kColO + s * kColOStride, tmem + kColP + 32 * s,
+                                   smem_desc_lo(smem_addr(sm.v[(n - 1) % kVStages])), idesc_pv, n > 1 ? 1u : 0u);
+                        mma_commit_elect(smem_addr(n < n_iters ? &sm.pv_done[s] : &sm.o_full[s]));
                     }
-                    __syncwarp();
                     OVC_TL(it, 12 + s * 6 + 2);
                 }
             }
             if (!ok) {
                 // Let MMAs already issued finish before tensor memory is released.
-                if (lane == 0) mma_commit(smem_addr(&sm.drain));
-                __syncwarp();
+                mma_commit_elect(smem_addr(&sm.drain));
                 const long long t0 = clock64();
                 while (!mbar_try_wait(smem_addr(&sm.drain), 0) && clock64() - t0 < kWaitCycles) {}
             }
         } else if (warp == 10) {
-            // ---------------- relay: TMA arrivals -> gate[0] ----------------
-            // gate[0] completion k lets the MMA warp issue QK with K(k+1) and PV with V(k).
+            // ---------------- relay: TMA arrivals -> gates ----------------
+            // gate[0] completion n precedes PV with V(n-1); gate[1] completion n precedes QK with K(n+1).
             if (lane == 0) {
-                for (int k = 0; k < n_iters; ++k) {
-                    if (!wait_bar(sm, &sm.v_full[k % kVStages], (k / kVStages) & 1, p.status)) break;
-                    if (k + 1 < n_iters &&
-                        !wait_bar(sm, &sm.k_full[(k + 1) % kKStages], ((k + 1) / kKStages) & 1, p.status))
-                        break;
-                    if (k > 0 && !wait_bar(sm, &sm.gate[0], (k - 1) & 1, p.status)) break;
+                for (int n = 0; n <= n_iters; ++n) {
+                    if (n > 0 && !wait_bar(sm, &sm.v_full[(n - 1) % kVStages], ((n - 1) / kVStages) & 1, p.status)) break;
+                    if (n > 0 && !wait_bar(sm, &sm.gate[0], (n - 1) & 1, p.status)) break;
                     mbar_arrive(smem_addr(&sm.gate[0]));
+                    if (n + 1 < n_iters &&
+                        !wait_bar(sm, &sm.k_full[(n + 1) % kKStages], ((n + 1) / kKStages) & 1, p.status))
+                        break;
+                    if (n > 0 && !wait_bar(sm, &sm.gate[1], (n - 1) & 1, p.status)) break;
+                    mbar_arrive(smem_addr(&sm.gate[1]));
                 }
             }
         }
@@ -378,13 +432,9 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         const float code_scale0 = sigma * 4.76837158203125e-07f;  // sigma * 8 * 2^-24
         const float* kd_row = p.k_descale + bh_l * p.n_tiles;
         const int tail_valid = static_cast<int>(p.Sk - static_cast<long long>(p.n_tiles - 1) * kTile);
-        const uint32_t gate_copied = smem_addr(&sm.gate[1 - stage]);  // "my scores left tensor memory"
-        const uint32_t gate_stored = smem_addr(&sm.gate[stage]);      // "my probabilities are stored"
+        const uint32_t my_gate = smem_addr(&sm.gate[stage]);  // "scores copied out, previous probabilities stored"
 
-        // gate[1] completion 0 has no "P1(-1) stored": stage 1 supplies those arrivals up front.
-        if (stage == 1) mbar_arrive(gate_stored);
-
-        float row_max = 0.0f, saved_denominator = 0.0f;
+        float row_max = 0.0f, bias = 0.0f, saved_denominator = 0.0f;
         bool ok = true;
         for (int it = 0; it < n_iters; ++it) {
             const int j = tile_at(it, j0, p.first_tile, p.n_tiles);
@@ -402,7 +452,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
             tmem_ld32(t_s + 96, s + 96);
             tmem_wait_ld();
             tc_fence_before();
-            mbar_arrive(gate_copied);
+            mbar_arrive(my_gate);
             if ((warp & 3) == 0) OVC_TL(it, stage * 6 + 2);
 
 #ifdef OVC_DEBUG_DUMP
@@ -428,43 +478,37 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
                     s[4 * c + 3] = __float_as_uint(__uint_as_float(s[4 * c + 3]) * f.w);
                 }
             }
-            // Row max of the tile, three inputs per instruction.
-            float m9[43];
-#pragma unroll
-            for (int c = 0; c < 42; ++c)
-                m9[c] = fmax3(__uint_as_float(s[3 * c]), __uint_as_float(s[3 * c + 1]), __uint_as_float(s[3 * c + 2]));
-            m9[42] = fmaxf(__uint_as_float(s[126]), __uint_as_float(s[127]));
-            float m3[15];
-#pragma unroll
-            for (int c = 0; c < 14; ++c) m3[c] = fmax3(m9[3 * c], m9[3 * c + 1], m9[3 * c + 2]);
-            m3[14] = m9[42];
-            float m1[5];
-#pragma unroll
-            for (int c = 0; c < 5; ++c) m1[c] = fmax3(m3[3 * c], m3[3 * c + 1], m3[3 * c + 2]);
-            const float tile_max = fmaxf(fmax3(m1[0], m1[1], m1[2]), fmaxf(m1[3], m1[4])) * kd;
+            // Codes against the running max, formed while the row max of this tile is still being
+            // reduced: in the steady state the max does not move and these are the final codes, so
+            // the conversion does not wait for the reduction.  Same formulas either way.
+            const float code_scale = code_scale0 * kd;
+            const uint64_t scale2 = pack2(code_scale, code_scale);
+            uint32_t codes[32];
+            if (it > 0) encode128(s, scale2, pack2(bias, bias), codes);
+            const float tile_max = max128(s) * kd;
 
             if ((warp & 3) == 0) OVC_TL(it, stage * 6 + 3);
-            float alpha = 0.0f;
-            float new_max = tile_max;
-            if (it > 0) {
-                new_max = fmaxf(row_max, tile_max);
-                const float safe = new_max == -INFINITY ? 0.0f : new_max;
-                alpha = ex2((row_max - safe) * sigma);
+            float alpha = 1.0f;
+            if (it == 0 || __any_sync(0xFFFFFFFFu, tile_max > row_max)) {
+                // The max moved for some row of the warp (or this is the first tile): new bias, new codes.
+                float new_max = tile_max;
+                alpha = 0.0f;
+                if (it > 0) {
+                    new_max = fmaxf(row_max, tile_max);
+                    const float safe = new_max == -INFINITY ? 0.0f : new_max;
+                    alpha = ex2((row_max - safe) * sigma);
+                }
+                row_max = new_max;
+                bias = expcast_bias(new_max == -INFINITY ? 0.0f : new_max, code_scale0);
+                encode128(s, scale2, pack2(bias, bias), codes);
             }
-            row_max = new_max;
-            const float safe_max = new_max == -INFINITY ? 0.0f : new_max;
-            const float bias = expcast_bias(safe_max, code_scale0);
-            const float code_scale = code_scale0 * kd;
-            const uint64_t scale2 = pack2(code_scale, code_scale), bias2 = pack2(bias, bias);
-            uint32_t codes[32];
-#pragma unroll
-            for (int c = 0; c < 32; ++c) codes[c] = encode4(s[4 * c], s[4 * c + 1], s[4 * c + 2], s[4 * c + 3], scale2, bias2);
             if (it > 0) {
                 // The stage's previous PV (step it-1) is issued after this step's QK, so the score
                 // barrier does not cover it: wait for it before P is overwritten or O is rescaled.
                 ok = __all_sync(0xFFFFFFFFu, wait_bar(sm, &sm.pv_done[stage], (it - 1) & 1, p.status));
                 if (!ok) break;
                 tc_fence_after();
+                if (warp == 4 && lane == 0) sm.progress[2] = it;  // V(it-1) is free: both stages' PV have read it
             }
             tmem_st32(t_p, codes);
             if ((warp & 3) == 0) OVC_TL(it, stage * 6 + 4);
@@ -498,12 +542,13 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
                 tmem_st1(t_o + kDim, __float_as_uint(l * alpha));
             }
             tmem_wait_st();
-            tc_fence_before();
-            mbar_arrive(gate_stored);
             if ((warp & 3) == 0) OVC_TL(it, stage * 6 + 5);
         }
-        // gate[1]'s last completion has no "S0 copied out": stage 0 supplies those arrivals.
-        if (ok && stage == 0) mbar_arrive(gate_copied);
+        // The last probabilities are stored; there are no further scores to copy out.
+        if (ok) {
+            tc_fence_before();
+            mbar_arrive(my_gate);
+        }
         if (ok) ok = __all_sync(0xFFFFFFFFu, wait_bar(sm, &sm.o_full[stage], 0, p.status));
         if (ok) {
             tc_fence_after();

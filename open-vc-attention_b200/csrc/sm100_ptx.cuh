@@ -154,6 +154,56 @@ __device__ __forceinline__ void mma_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
 
+// Four K-steps of one 128-wide MMA, issued by one elected lane while the whole warp executes the
+// (convergent) code, so that descriptors and addresses stay warp-uniform values.  `a_lo` / `b_lo` are
+// the low words of shared-memory descriptors (high word kSmemDescHi); K advances 32 bytes per step.
+constexpr uint32_t kSmemDescHi = (1024u >> 4) | (1u << 14) | (2u << 29);
+__device__ __forceinline__ uint32_t smem_desc_lo(uint32_t saddr) { return ((saddr & 0x3FFFFu) >> 4) | (1u << 16); }
+
+__device__ __forceinline__ void mma4_f8_ss(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t idesc) {
+    asm volatile(
+        "{\n\t.reg .pred leader;\n\t.reg .b64 da, db;\n\t.reg .b32 al, bl;\n\t"
+        "elect.sync _|leader, 0xFFFFFFFF;\n\t"
+        "mov.b64 da, {%1, %3};\n\tmov.b64 db, {%2, %3};\n\t"
+        "@leader tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], da, db, %4, 0;\n\t"
+        "add.u32 al, %1, 2;\n\tadd.u32 bl, %2, 2;\n\tmov.b64 da, {al, %3};\n\tmov.b64 db, {bl, %3};\n\t"
+        "@leader tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], da, db, %4, 1;\n\t"
+        "add.u32 al, %1, 4;\n\tadd.u32 bl, %2, 4;\n\tmov.b64 da, {al, %3};\n\tmov.b64 db, {bl, %3};\n\t"
+        "@leader tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], da, db, %4, 1;\n\t"
+        "add.u32 al, %1, 6;\n\tadd.u32 bl, %2, 6;\n\tmov.b64 da, {al, %3};\n\tmov.b64 db, {bl, %3};\n\t"
+        "@leader tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], da, db, %4, 1;\n\t}"
+        :
+        : "r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(kSmemDescHi), "r"(idesc)
+        : "memory");
+}
+// Same with A in tensor memory (8 columns per K-step); `accumulate_first` = 0 starts a new accumulation.
+__device__ __forceinline__ void mma4_f8_ts(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo, uint32_t idesc,
+                                           uint32_t accumulate_first) {
+    asm volatile(
+        "{\n\t.reg .pred leader, p;\n\t.reg .b64 db;\n\t.reg .b32 bl, ta;\n\t"
+        "elect.sync _|leader, 0xFFFFFFFF;\n\t"
+        "setp.ne.b32 p, %5, 0;\n\t"
+        "mov.b64 db, {%2, %3};\n\t"
+        "@leader tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], [%1], db, %4, p;\n\t"
+        "add.u32 bl, %2, 2;\n\tadd.u32 ta, %1, 8;\n\tmov.b64 db, {bl, %3};\n\t"
+        "@leader tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], [ta], db, %4, 1;\n\t"
+        "add.u32 bl, %2, 4;\n\tadd.u32 ta, %1, 16;\n\tmov.b64 db, {bl, %3};\n\t"
+        "@leader tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], [ta], db, %4, 1;\n\t"
+        "add.u32 bl, %2, 6;\n\tadd.u32 ta, %1, 24;\n\tmov.b64 db, {bl, %3};\n\t"
+        "@leader tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], [ta], db, %4, 1;\n\t}"
+        :
+        : "r"(d_tmem), "r"(a_tmem), "r"(b_lo), "r"(kSmemDescHi), "r"(idesc), "r"(accumulate_first)
+        : "memory");
+}
+__device__ __forceinline__ void mma_commit_elect(uint32_t bar) {
+    asm volatile(
+        "{\n\t.reg .pred leader;\n\t"
+        "elect.sync _|leader, 0xFFFFFFFF;\n\t"
+        "@leader tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t}"
+        ::"r"(bar)
+        : "memory");
+}
+
 // Instruction descriptor for kind::f8f6f4, E4M3 x E4M3 -> F32, both operands K-major, M = 128.
 __host__ __device__ constexpr uint32_t idesc_e4m3_f32(int n) {
     return (1u << 4)                              // accumulator format F32
