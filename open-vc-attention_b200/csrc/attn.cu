@@ -39,7 +39,7 @@
 #define OVC_ENCODE_SCALAR 0
 #endif
 #ifndef OVC_MAX3
-#define OVC_MAX3 0
+#define OVC_MAX3 1
 #endif
 
 namespace ovc {
@@ -100,18 +100,25 @@ __device__ __forceinline__ void give_up(SmemLayout& sm, uint32_t* status) {
     if (status != nullptr) atomicOr(status, OVC_STATUS_WAIT_EXPIRED);
 }
 
-// Bounded wait.  Returns false when the barrier did not complete in time or another thread of
-// the CTA already gave up; the caller then leaves its loop and the CTA tears down.
+// Bounded wait.  The hardware suspends the thread inside try_wait while the phase is pending, so a
+// waiting warp issues almost nothing; the abort flag and the clock are looked at only every 16th
+// wake-up.  Returns false when the barrier did not complete in time or another thread of the CTA
+// already gave up; the caller then leaves its loop and the CTA tears down.
 __device__ __forceinline__ bool wait_bar(SmemLayout& sm, uint64_t* bar, uint32_t parity, uint32_t* status) {
     const uint32_t addr = smem_addr(bar);
     if (mbar_try_wait(addr, parity)) return true;
-    const long long start = clock64();
-    while (true) {
+    long long start = 0;
+#pragma unroll 1
+    for (uint32_t tries = 1;; ++tries) {
         if (mbar_try_wait_sleep(addr, parity, kSleepHintNs)) return true;
-        if (sm.abort_flag) return false;
-        if (clock64() - start > kWaitCycles) {
-            give_up(sm, status);
-            return false;
+        if ((tries & 15u) == 0) {
+            if (sm.abort_flag) return false;
+            const long long now = clock64();
+            if (start == 0) start = now;
+            if (now - start > kWaitCycles) {
+                give_up(sm, status);
+                return false;
+            }
         }
     }
 }
@@ -126,7 +133,7 @@ __device__ __forceinline__ bool wait_progress(SmemLayout& sm, int which, int tar
             give_up(sm, status);
             return false;
         }
-        __nanosleep(64);
+        __nanosleep(256);
     }
     return true;
 }
