@@ -64,13 +64,13 @@ struct SmemLayout {
     alignas(1024) uint8_t v[kVStages][kVSlotBytes];
     alignas(8) uint64_t q_full[2];
     uint64_t k_full[kKStages], v_full[kVStages];
+    uint64_t k_empty[kKStages], v_empty[kVStages];  // slot may be refilled (one arrival by a stage-1 thread)
     uint64_t s_full[2];   // scores of a stage are in tensor memory (commit)
     uint64_t gate[2];     // what the MMA warp waits for before a stage's group
     uint64_t pv_done[2];  // the stage's previous PV has been accumulated (commit)
     uint64_t o_full[2], drain;
     uint32_t tmem_base;
     volatile uint32_t abort_flag;
-    volatile int progress[3];  // [0],[1]: s_full phases seen by stage 0 / 1; [2]: PV steps of stage 1 seen done
 };
 
 struct AttnParams {
@@ -121,21 +121,6 @@ __device__ __forceinline__ bool wait_bar(SmemLayout& sm, uint64_t* bar, uint32_t
             }
         }
     }
-}
-
-// Bounded wait until a progress counter reaches `target`.
-__device__ __forceinline__ bool wait_progress(SmemLayout& sm, int which, int target, uint32_t* status) {
-    if (sm.progress[which] >= target) return true;
-    const long long start = clock64();
-    while (sm.progress[which] < target) {
-        if (sm.abort_flag) return false;
-        if (clock64() - start > kWaitCycles) {
-            give_up(sm, status);
-            return false;
-        }
-        __nanosleep(256);
-    }
-    return true;
 }
 
 #ifdef OVC_DEBUG_DUMP
@@ -291,15 +276,18 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
             mbar_init(smem_addr(&sm.pv_done[i]), 1);
             mbar_init(smem_addr(&sm.o_full[i]), 1);
         }
-        for (int i = 0; i < kKStages; ++i) mbar_init(smem_addr(&sm.k_full[i]), 1);
-        for (int i = 0; i < kVStages; ++i) mbar_init(smem_addr(&sm.v_full[i]), 1);
+        for (int i = 0; i < kKStages; ++i) {
+            mbar_init(smem_addr(&sm.k_full[i]), 1);
+            mbar_init(smem_addr(&sm.k_empty[i]), 1);
+        }
+        for (int i = 0; i < kVStages; ++i) {
+            mbar_init(smem_addr(&sm.v_full[i]), 1);
+            mbar_init(smem_addr(&sm.v_empty[i]), 1);
+        }
         mbar_init(smem_addr(&sm.gate[0]), 129);  // 128 conversion threads of the stage + the relay
         mbar_init(smem_addr(&sm.gate[1]), 129);
         mbar_init(smem_addr(&sm.drain), 1);
         sm.abort_flag = 0;
-        sm.progress[0] = 0;
-        sm.progress[1] = 0;
-        sm.progress[2] = 0;
         mbar_init_fence();
     }
     // Rows 128.. of every V slot: E4M3 1.0, so PV also accumulates the row sums of P.
@@ -335,13 +323,19 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
                 for (int it = 0; it < n_iters; ++it) {
                     const int j = tile_at(it, j0, p.first_tile, p.n_tiles);
                     const int ks = it % kKStages, vs = it % kVStages;
-                    // K(it - kKStages) was last read by stage 1's QK of that step.
-                    if (!wait_progress(sm, 1, it - kKStages + 1, p.status)) break;
+                    // K(it - kKStages) was last read by stage 1's QK of that step; stage 1 releases the slot
+                    // when it sees those scores.
+                    if (it >= kKStages &&
+                        !wait_bar(sm, &sm.k_empty[ks], (it / kKStages - 1) & 1, p.status))
+                        break;
                     mbar_expect_tx(smem_addr(&sm.k_full[ks]), kTileBytes);
                     tma_load_4d(smem_addr(sm.k[ks]), &tmap_k, smem_addr(&sm.k_full[ks]), 0, head, j * kTile, batch, keep);
                     issued_k = it + 1;
-                    // V(it - kVStages) was last read by stage 1's PV of that step.
-                    if (!wait_progress(sm, 2, it - kVStages + 1, p.status)) break;
+                    // V(it - kVStages) was last read by stage 1's PV of that step; stage 1 releases the slot
+                    // when it sees that PV done.
+                    if (it >= kVStages &&
+                        !wait_bar(sm, &sm.v_empty[vs], (it / kVStages - 1) & 1, p.status))
+                        break;
                     mbar_expect_tx(smem_addr(&sm.v_full[vs]), kTileBytes);
                     tma_load_4d(smem_addr(sm.v[vs]), &tmap_v, smem_addr(&sm.v_full[vs]), j * kTile, 0, head, batch, keep);
                     issued_v = it + 1;
@@ -451,7 +445,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
             if (!ok) break;
             if ((warp & 3) == 0) OVC_TL(it, stage * 6 + 1);
             tc_fence_after();
-            if ((warp & 3) == 0 && lane == 0) sm.progress[stage] = it + 1;
+            if (warp == 4 && lane == 0) mbar_arrive(smem_addr(&sm.k_empty[it % kKStages]));  // K(it) has been read
             uint32_t s[128];
             tmem_ld32(t_s, s);
             tmem_ld32(t_s + 32, s + 32);
@@ -515,7 +509,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
                 ok = __all_sync(0xFFFFFFFFu, wait_bar(sm, &sm.pv_done[stage], (it - 1) & 1, p.status));
                 if (!ok) break;
                 tc_fence_after();
-                if (warp == 4 && lane == 0) sm.progress[2] = it;  // V(it-1) is free: both stages' PV have read it
+                if (warp == 4 && lane == 0) mbar_arrive(smem_addr(&sm.v_empty[(it - 1) % kVStages]));  // V(it-1) has been read
             }
             tmem_st32(t_p, codes);
             if ((warp & 3) == 0) OVC_TL(it, stage * 6 + 4);
