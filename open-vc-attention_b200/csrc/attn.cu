@@ -179,35 +179,25 @@ __device__ __forceinline__ uint64_t pack_u2(uint32_t lo, uint32_t hi) {
     asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "r"(lo), "r"(hi));
     return r;
 }
-__device__ __forceinline__ uint32_t half_codes(uint64_t y) {
-    uint32_t lo, hi, h;
-    asm("mov.b64 {%0, %1}, %2;" : "=r"(lo), "=r"(hi) : "l"(y));
-    asm("cvt.rn.relu.f16x2.f32 %0, %1, %2;" : "=r"(h) : "f"(__uint_as_float(hi)), "f"(__uint_as_float(lo)));
-    return h;
+// Two FP16-subnormal conversions give (c2:c0) and (c3:c1) with each code in the low byte of a half;
+// one integer multiply-add (the FMA pipe, which has room) merges them into c0|c1<<8|c2<<16|c3<<24.
+__device__ __forceinline__ uint32_t codes4(uint64_t y01, uint64_t y23) {
+    uint32_t y0, y1, y2, y3, a, b, r;
+    asm("mov.b64 {%0, %1}, %2;" : "=r"(y0), "=r"(y1) : "l"(y01));
+    asm("mov.b64 {%0, %1}, %2;" : "=r"(y2), "=r"(y3) : "l"(y23));
+    asm("cvt.rn.relu.f16x2.f32 %0, %1, %2;" : "=r"(a) : "f"(__uint_as_float(y2)), "f"(__uint_as_float(y0)));
+    asm("cvt.rn.relu.f16x2.f32 %0, %1, %2;" : "=r"(b) : "f"(__uint_as_float(y3)), "f"(__uint_as_float(y1)));
+    asm("mad.lo.u32 %0, %1, 256, %2;" : "=r"(r) : "r"(b), "r"(a));
+    return r;
 }
 __device__ __forceinline__ void encode128(const uint32_t (&s)[128], uint64_t scale2, uint64_t bias2, uint32_t (&codes)[32]) {
 #pragma unroll
     for (int c = 0; c < 4; ++c) {
-        uint32_t h[16];
-#if OVC_ENCODE_SCALAR
-        float sc, bi, dummy;
-        asm("mov.b64 {%0, %1}, %2;" : "=f"(sc), "=f"(dummy) : "l"(scale2));
-        asm("mov.b64 {%0, %1}, %2;" : "=f"(bi), "=f"(dummy) : "l"(bias2));
-        float y[32];
-#pragma unroll
-        for (int i = 0; i < 32; ++i) y[i] = fmaf(__uint_as_float(s[32 * c + i]), sc, bi);
-#pragma unroll
-        for (int i = 0; i < 16; ++i)
-            asm("cvt.rn.relu.f16x2.f32 %0, %1, %2;" : "=r"(h[i]) : "f"(y[2 * i + 1]), "f"(y[2 * i]));
-#else
         uint64_t y[16];
 #pragma unroll
         for (int i = 0; i < 16; ++i) y[i] = ffma2(pack_u2(s[32 * c + 2 * i], s[32 * c + 2 * i + 1]), scale2, bias2);
 #pragma unroll
-        for (int i = 0; i < 16; ++i) h[i] = half_codes(y[i]);
-#endif
-#pragma unroll
-        for (int i = 0; i < 8; ++i) codes[8 * c + i] = __byte_perm(h[2 * i], h[2 * i + 1], 0x6420);
+        for (int i = 0; i < 8; ++i) codes[8 * c + i] = codes4(y[2 * i], y[2 * i + 1]);
     }
 }
 
