@@ -104,10 +104,22 @@ struct BlockQuantArgs {
     float* amax_init;  // optional [H]: reset to 0 by the (block 0, source 0) CTAs
 };
 
+// Max over the 256 threads of a CTA; every thread gets the result.
+__device__ __forceinline__ float cta256_max(float m) {
+    __shared__ float part[8];
+    m = warp_max(m);
+    if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = m;
+    __syncthreads();
+    return fmaxf(fmaxf(fmaxf(part[0], part[1]), fmaxf(part[2], part[3])),
+                 fmaxf(fmaxf(part[4], part[5]), fmaxf(part[6], part[7])));
+}
+
 // One CTA = one (128-token block, head) tile of 128x128 16-bit values held in registers:
-// 16 rows per thread, 16 bytes per row.  grid (blocks, H, B*sources).
+// 256 threads, 8 rows per thread, 16 bytes per row (32 registers of raw data per thread, so that
+// several CTAs are resident per SM and their load, reduce and store phases overlap).
+// grid (blocks, H, B*sources).
 template <int DT>
-__global__ void __launch_bounds__(128) quant_block_kernel(BlockQuantArgs a, long long S, int H, int blocks) {
+__global__ void __launch_bounds__(256, 3) quant_block_kernel(BlockQuantArgs a, long long S, int H, int blocks) {
     const int which = blockIdx.z % a.sources;
     const long long batch = blockIdx.z / a.sources;
     const int blk = blockIdx.x, head = blockIdx.y;
@@ -116,20 +128,20 @@ __global__ void __launch_bounds__(128) quant_block_kernel(BlockQuantArgs a, long
     const long long first = static_cast<long long>(blk) * kTile + r0;
     const uint16_t* src = static_cast<const uint16_t*>(a.x[which]) + batch * S * row_pitch + head * kDim + c16 * 8;
 
-    uint4 raw[16];
+    uint4 raw[8];
 #pragma unroll
-    for (int i = 0; i < 16; ++i) {
-        const long long row = first + 8 * i;
+    for (int i = 0; i < 8; ++i) {
+        const long long row = first + 16 * i;
         raw[i] = row < S ? ld_stream(src + row * row_pitch) : make_uint4(0, 0, 0, 0);
     }
     float m = 0.0f;
 #pragma unroll
-    for (int i = 0; i < 16; ++i) {
+    for (int i = 0; i < 8; ++i) {
         float f[8];
         widen8<DT>(raw[i], f);
         m = absmax8(f, m);
     }
-    const float amax = fmaxf(cta128_max(m), kFloor);
+    const float amax = fmaxf(cta256_max(m), kFloor);
     const float scale = __fdiv_rn(kQMax, amax);
     if (threadIdx.x == 0) {
         float* d = a.descale[which] + (batch * H + head) * a.descale_stride[which];
@@ -139,8 +151,8 @@ __global__ void __launch_bounds__(128) quant_block_kernel(BlockQuantArgs a, long
     }
     uint8_t* dst = a.codes[which] + batch * S * row_pitch + head * kDim + c16 * 8;
 #pragma unroll
-    for (int i = 0; i < 16; ++i) {
-        const long long row = first + 8 * i;
+    for (int i = 0; i < 8; ++i) {
+        const long long row = first + 16 * i;
         if (row < S) {
             float f[8];
             widen8<DT>(raw[i], f);
@@ -443,8 +455,8 @@ int ovc_quantize_per_block(const void* x, int dtype, int64_t B, int64_t S, int64
     a.sources = 1, a.amax_init = nullptr;
     const dim3 grid(static_cast<unsigned>(blocks), static_cast<unsigned>(H), static_cast<unsigned>(B));
     auto s = static_cast<cudaStream_t>(stream);
-    if (dtype == OVC_BF16) quant_block_kernel<OVC_BF16><<<grid, 128, 0, s>>>(a, S, static_cast<int>(H), static_cast<int>(blocks));
-    else quant_block_kernel<OVC_F16><<<grid, 128, 0, s>>>(a, S, static_cast<int>(H), static_cast<int>(blocks));
+    if (dtype == OVC_BF16) quant_block_kernel<OVC_BF16><<<grid, 256, 0, s>>>(a, S, static_cast<int>(H), static_cast<int>(blocks));
+    else quant_block_kernel<OVC_F16><<<grid, 256, 0, s>>>(a, S, static_cast<int>(H), static_cast<int>(blocks));
     return check_launch();
 }
 
@@ -494,11 +506,11 @@ int ovc_prepare_fused(const void* q, const void* k, const void* v, int dtype, in
     const dim3 grid_qk(static_cast<unsigned>(blocks), static_cast<unsigned>(H), 2);
     const dim3 grid_v(static_cast<unsigned>(blocks), static_cast<unsigned>(H), 1);
     if (dtype == OVC_BF16) {
-        quant_block_kernel<OVC_BF16><<<grid_qk, 128, 0, s>>>(a, S, h, static_cast<int>(blocks));
+        quant_block_kernel<OVC_BF16><<<grid_qk, 256, 0, s>>>(a, S, h, static_cast<int>(blocks));
         head_amax_kernel<OVC_BF16><<<grid_v, 128, 0, s>>>(v, amax_ws, S, h);
         cast_pack_kernel<OVC_BF16><<<grid_v, 256, 0, s>>>(v, amax_ws, static_cast<uint8_t*>(v_packed), v_descale, S, h, S_pad);
     } else {
-        quant_block_kernel<OVC_F16><<<grid_qk, 128, 0, s>>>(a, S, h, static_cast<int>(blocks));
+        quant_block_kernel<OVC_F16><<<grid_qk, 256, 0, s>>>(a, S, h, static_cast<int>(blocks));
         head_amax_kernel<OVC_F16><<<grid_v, 128, 0, s>>>(v, amax_ws, S, h);
         cast_pack_kernel<OVC_F16><<<grid_v, 256, 0, s>>>(v, amax_ws, static_cast<uint8_t*>(v_packed), v_descale, S, h, S_pad);
     }
