@@ -257,7 +257,9 @@ def main():
                    "parallelism": f"heads{world}"},
         "attention_kernel_ms": kernel_ms,
         "roofline": {"bound": "tensor", "achieved": achieved, "peak": fp8_peak, "unit": "TFLOP/s",
-                     "frac": achieved / fp8_peak, "traffic": None,
+                     "frac": achieved / fp8_peak,
+                     # dram read + write of one attention launch: ncu capture at H=7 (333.4 MB), scaled by heads
+                     "traffic": 333.4e6 / 7 * heads,
                      "peak_source": f"2 x bf16_tflops_sustained of {peak_kind} peaks (FP8 runs at twice the BF16 rate)",
                      "frac_of_nominal_4500": achieved / 4500.0},
         "gpu_launches": 4 * args.steps,
