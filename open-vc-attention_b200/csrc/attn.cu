@@ -35,9 +35,6 @@
 #include "common.cuh"
 #include "sm100_ptx.cuh"
 
-#ifndef OVC_ENCODE_SCALAR
-#define OVC_ENCODE_SCALAR 0
-#endif
 #ifndef OVC_MAX3
 #define OVC_MAX3 1
 #endif
@@ -201,7 +198,7 @@ __device__ __forceinline__ void encode128(const uint32_t (&s)[128], uint64_t sca
     }
 }
 
-// Row max of 128 scores by a level-wise tree of two-input max (full-rate pipe).
+// Row max of 128 scores: three-input max tree (64 instructions); OVC_MAX3=0 selects a two-input tree.
 __device__ __forceinline__ float max128(const uint32_t (&s)[128]) {
 #if OVC_MAX3
     float m9[43];
@@ -217,7 +214,7 @@ __device__ __forceinline__ float max128(const uint32_t (&s)[128]) {
 #pragma unroll
     for (int c = 0; c < 5; ++c) m1[c] = fmax3(m3[3 * c], m3[3 * c + 1], m3[3 * c + 2]);
     return fmaxf(fmax3(m1[0], m1[1], m1[2]), fmaxf(m1[3], m1[4]));
-#endif
+#else
     float m[64];
 #pragma unroll
     for (int i = 0; i < 64; ++i) m[i] = fmaxf(__uint_as_float(s[i]), __uint_as_float(s[i + 64]));
@@ -226,6 +223,7 @@ __device__ __forceinline__ float max128(const uint32_t (&s)[128]) {
 #pragma unroll
         for (int i = 0; i < w; ++i) m[i] = fmaxf(m[i], m[i + w]);
     return m[0];
+#endif
 }
 
 __device__ __forceinline__ uint32_t bf16x2(float lo, float hi) {
@@ -365,7 +363,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
             // gate[s] completion n: stage s has copied S_s(n) out (n < N) and stored P_s(n-1) (n > 0).
             // Then: scores of the other stage's next step (stage 1: step n, stage 0: step n+1), PV_s(n-1).
             for (int n = 0; ok && n <= n_iters; ++n) {
-                const int it = n;
+                [[maybe_unused]] const int it = n;  // step index for debug stamps
                 for (int s = 0; s < 2; ++s) {
                     OVC_TL(it, 12 + s * 6 + 0);
                     ok = __all_sync(0xFFFFFFFFu, wait_bar(sm, &sm.gate[s], n & 1, p.status));
