@@ -104,9 +104,9 @@ struct BlockQuantArgs {
     float* amax_init;  // optional [H]: reset to 0 by the (block 0, source 0) CTAs
 };
 
-// Max over the 256 threads of a CTA; every thread gets the result.
-__device__ __forceinline__ float cta256_max(float m) {
-    __shared__ float part[8];
+// Max over the 256 threads of a CTA; every thread gets the result.  `part` is caller-provided shared
+// memory (8 floats) so that consecutive reductions can alternate between two buffers.
+__device__ __forceinline__ float cta256_max(float m, float* part) {
     m = warp_max(m);
     if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = m;
     __syncthreads();
@@ -114,50 +114,65 @@ __device__ __forceinline__ float cta256_max(float m) {
                  fmaxf(fmaxf(part[4], part[5]), fmaxf(part[6], part[7])));
 }
 
-// One CTA = one (128-token block, head) tile of 128x128 16-bit values held in registers:
-// 256 threads, 8 rows per thread, 16 bytes per row (32 registers of raw data per thread, so that
-// several CTAs are resident per SM and their load, reduce and store phases overlap).
-// grid (blocks, H, B*sources).
+constexpr int kBlocksPerCta = 4;  // consecutive 128-token blocks handled by one CTA of the Q/K quantiser
+
+// Q/K quantiser.  One CTA walks kBlocksPerCta consecutive (128-token block, head) tiles of 128x128
+// 16-bit values: 256 threads, 8 rows per thread, 16 bytes per row, the tile held in registers.  The
+// loads of the next tile are issued before the current tile is reduced and stored, so the CTA barrier
+// of the amax reduction does not leave the memory system idle.  grid (ceil(blocks/4), H, B*sources).
 template <int DT>
-__global__ void __launch_bounds__(256, 3) quant_block_kernel(BlockQuantArgs a, long long S, int H, int blocks) {
+__global__ void __launch_bounds__(256, 2) quant_block_kernel(BlockQuantArgs a, long long S, int H, int blocks) {
+    __shared__ float part[2][8];
     const int which = blockIdx.z % a.sources;
     const long long batch = blockIdx.z / a.sources;
-    const int blk = blockIdx.x, head = blockIdx.y;
+    const int head = blockIdx.y;
     const int c16 = threadIdx.x & 15, r0 = threadIdx.x >> 4;
     const long long row_pitch = static_cast<long long>(H) * kDim;  // elements
-    const long long first = static_cast<long long>(blk) * kTile + r0;
     const uint16_t* src = static_cast<const uint16_t*>(a.x[which]) + batch * S * row_pitch + head * kDim + c16 * 8;
+    uint8_t* dst = a.codes[which] + batch * S * row_pitch + head * kDim + c16 * 8;
+    float* descale = a.descale[which] + (batch * H + head) * a.descale_stride[which];
+    const int first_blk = blockIdx.x * kBlocksPerCta;
+    const int last_blk = min(first_blk + kBlocksPerCta, blocks);
 
-    uint4 raw[8];
+    uint4 raw[8], next[8];
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
-        const long long row = first + 16 * i;
+        const long long row = static_cast<long long>(first_blk) * kTile + r0 + 16 * i;
         raw[i] = row < S ? ld_stream(src + row * row_pitch) : make_uint4(0, 0, 0, 0);
     }
-    float m = 0.0f;
+    for (int blk = first_blk; blk < last_blk; ++blk) {
+        if (blk + 1 < last_blk) {
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-        float f[8];
-        widen8<DT>(raw[i], f);
-        m = absmax8(f, m);
-    }
-    const float amax = fmaxf(cta256_max(m), kFloor);
-    const float scale = __fdiv_rn(kQMax, amax);
-    if (threadIdx.x == 0) {
-        float* d = a.descale[which] + (batch * H + head) * a.descale_stride[which];
-        d[blk] = __fdiv_rn(amax, kQMax);
-        if (blk == 0 && a.descale_stride[which] > blocks) d[blocks] = 1.0f;
-        if (blk == 0 && which == 0 && a.amax_init != nullptr) a.amax_init[batch * H + head] = 0.0f;
-    }
-    uint8_t* dst = a.codes[which] + batch * S * row_pitch + head * kDim + c16 * 8;
+            for (int i = 0; i < 8; ++i) {
+                const long long row = static_cast<long long>(blk + 1) * kTile + r0 + 16 * i;
+                next[i] = row < S ? ld_stream(src + row * row_pitch) : make_uint4(0, 0, 0, 0);
+            }
+        }
+        float m = 0.0f;
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-        const long long row = first + 16 * i;
-        if (row < S) {
+        for (int i = 0; i < 8; ++i) {
             float f[8];
             widen8<DT>(raw[i], f);
-            *reinterpret_cast<uint2*>(dst + row * row_pitch) = quantize8(f, scale);
+            m = absmax8(f, m);
         }
+        const float amax = fmaxf(cta256_max(m, part[blk & 1]), kFloor);
+        const float scale = __fdiv_rn(kQMax, amax);
+        if (threadIdx.x == 0) {
+            descale[blk] = __fdiv_rn(amax, kQMax);
+            if (blk == 0 && a.descale_stride[which] > blocks) descale[blocks] = 1.0f;
+            if (blk == 0 && which == 0 && a.amax_init != nullptr) a.amax_init[batch * H + head] = 0.0f;
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const long long row = static_cast<long long>(blk) * kTile + r0 + 16 * i;
+            if (row < S) {
+                float f[8];
+                widen8<DT>(raw[i], f);
+                *reinterpret_cast<uint2*>(dst + row * row_pitch) = quantize8(f, scale);
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) raw[i] = next[i];
     }
 }
 
@@ -453,7 +468,7 @@ int ovc_quantize_per_block(const void* x, int dtype, int64_t B, int64_t S, int64
     BlockQuantArgs a{};
     a.x[0] = x, a.codes[0] = static_cast<uint8_t*>(codes), a.descale[0] = descale, a.descale_stride[0] = descale_stride;
     a.sources = 1, a.amax_init = nullptr;
-    const dim3 grid(static_cast<unsigned>(blocks), static_cast<unsigned>(H), static_cast<unsigned>(B));
+    const dim3 grid(static_cast<unsigned>(ceil_div(blocks, kBlocksPerCta)), static_cast<unsigned>(H), static_cast<unsigned>(B));
     auto s = static_cast<cudaStream_t>(stream);
     if (dtype == OVC_BF16) quant_block_kernel<OVC_BF16><<<grid, 256, 0, s>>>(a, S, static_cast<int>(H), static_cast<int>(blocks));
     else quant_block_kernel<OVC_F16><<<grid, 256, 0, s>>>(a, S, static_cast<int>(H), static_cast<int>(blocks));
@@ -503,7 +518,7 @@ int ovc_prepare_fused(const void* q, const void* k, const void* v, int dtype, in
     a.descale[0] = q_descale, a.descale[1] = k_descale;
     a.descale_stride[0] = q_blocks, a.descale_stride[1] = blocks;
     a.sources = 2, a.amax_init = amax_ws;
-    const dim3 grid_qk(static_cast<unsigned>(blocks), static_cast<unsigned>(H), 2);
+    const dim3 grid_qk(static_cast<unsigned>(ceil_div(blocks, kBlocksPerCta)), static_cast<unsigned>(H), 2);
     const dim3 grid_v(static_cast<unsigned>(blocks), static_cast<unsigned>(H), 1);
     if (dtype == OVC_BF16) {
         quant_block_kernel<OVC_BF16><<<grid_qk, 256, 0, s>>>(a, S, h, static_cast<int>(blocks));

@@ -133,3 +133,29 @@ def test_repair_validation():
     wrong = dataclasses.replace(prepared, repair_k_descale=prepared.repair_k_descale[..., :100].contiguous())
     with pytest.raises(ValueError, match="repair_k_descale"):
         ovc.attention_v_repair(wrong)
+
+
+def test_repair_at_the_benchmark_size():
+    """[73397,14,128], Student-t V, budget 0.005: 367 tokens in 384 rows per head; zeroed repair rows give
+    the plain output bit for bit; with the residuals in place the error against exact attention drops."""
+    ovc, api, forward, v_repair = _mods()
+    from open_vc_attn.synthetic import student_t_values
+
+    s, h = 73397, 14
+    g = torch.Generator(device=DEV).manual_seed(73)
+    q, k = [torch.randn(s, h, 128, generator=g, device=DEV).to(torch.bfloat16) for _ in range(2)]
+    v = student_t_values(s, h, seed=74, device=DEV)
+    prepared = ovc.prepare_v_repair(q, k, v, budget=0.005)
+    assert (prepared.selected_tokens, prepared.repair_tokens) == (367, 384)
+    assert prepared.k.shape[0] == s + 384 and prepared.repair_k_descale.shape == (1, h, 384)
+    repaired = ovc.attention_v_repair(prepared)
+    plain = ovc.attention(q, k, v)
+    forward.check_status(q.device)
+    head, rows = 5, torch.arange(0, s, 997, device=DEV)
+    exact = oatt.exact_attention(f32(q[rows][:, head : head + 1]), f32(k[:, head : head + 1]), f32(v[:, head : head + 1]))
+    assert oatt.relative_l2(f32(repaired[rows][:, head : head + 1]), exact) < oatt.relative_l2(
+        f32(plain[rows][:, head : head + 1]), exact)
+    padded = (s + 384 + 127) // 128 * 128
+    buffer = torch.empty(0, dtype=torch.uint8, device=DEV).set_(prepared.v.untyped_storage(), 0, (h, 128, padded))
+    buffer[:, :, :384] = 0
+    assert torch.equal(ovc.attention_v_repair(prepared), plain)

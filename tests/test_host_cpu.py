@@ -157,3 +157,33 @@ def test_gather_heads_with_two_gloo_ranks(heads):
         p.join(120)
         assert p.exitcode == 0
     assert result[0] and result[1]
+
+
+def test_packed_segment_validation():
+    # tests/cpu/test_contracts.py:75-83 of the reference
+    from open_vc_attn.integrations.packed import segments
+
+    assert segments((0, 129, 258), 258, 129) == [(0, 129, False), (129, 258, False)]
+    assert segments((0, 129, 258), 258, 129, trailing_padding=True) == [(0, 129, False), (129, 258, True)]
+    for bad in (None, (0,), (1, 5), (0, 5, 5, 9), (0, 4.0, 9), (0, 3)):
+        with pytest.raises(ValueError):
+            segments(bad, 9, 9)
+    with pytest.raises(ValueError):
+        segments((0, 5, 9), 9, 4)
+
+
+def test_diffusion_adapter_argument_policy(monkeypatch):
+    pytest.importorskip("torch")
+    from open_vc_attn.integrations.diffusion import DenseDiffusionAdapter
+
+    monkeypatch.delenv("OPEN_VC_ATTN_IMPLEMENTATION", raising=False)
+    monkeypatch.delenv("OPEN_VC_ATTN_MODE", raising=False)
+    adapter = DenseDiffusionAdapter(2, 128, 0.1)
+    assert (adapter.version, adapter.mode, adapter.scale) == ("open-vc", "expcast", 0.1)
+    with pytest.raises(ValueError, match="head_size=128"):
+        DenseDiffusionAdapter(2, 64, 0.1)
+    with pytest.raises(ValueError, match="noncausal"):
+        DenseDiffusionAdapter(2, 128, 0.1, causal=True)
+    monkeypatch.setenv("OPEN_VC_ATTN_MODE", "bf16")
+    with pytest.raises(ValueError, match="reference with bf16"):
+        DenseDiffusionAdapter(2, 128, 0.1)
