@@ -127,36 +127,11 @@ __device__ __forceinline__ void tmem_st1(uint32_t taddr, uint32_t r) {
 }
 
 // ---- tcgen05 MMA, FP8 E4M3 x E4M3 -> FP32, one CTA -------------------------------------------
-// D[tmem] (+)= A[smem desc] * B[smem desc]
-__device__ __forceinline__ void mma_f8_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
-                                          uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}"
-        :
-        : "r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
-        : "memory");
-}
-// D[tmem] (+)= A[tmem] * B[smem desc]
-__device__ __forceinline__ void mma_f8_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
-                                          uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], [%1], %2, %3, p;\n\t}"
-        :
-        : "r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
-        : "memory");
-}
-// Arrive on an mbarrier once every MMA issued so far by this thread has completed.
-__device__ __forceinline__ void mma_commit(uint32_t bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-
 // Four K-steps of one 128-wide MMA, issued by one elected lane while the whole warp executes the
 // (convergent) code, so that descriptors and addresses stay warp-uniform values.  `a_lo` / `b_lo` are
-// the low words of shared-memory descriptors (high word kSmemDescHi); K advances 32 bytes per step.
+// the low words of shared-memory matrix descriptors: K-major rows of 128 bytes in the 128-byte swizzle,
+// 8-row groups 1024 bytes apart (tile base 1024-byte aligned), high word kSmemDescHi; K advances 32 bytes
+// (2 in descriptor units) per step.
 constexpr uint32_t kSmemDescHi = (1024u >> 4) | (1u << 14) | (2u << 29);
 __device__ __forceinline__ uint32_t smem_desc_lo(uint32_t saddr) { return ((saddr & 0x3FFFFu) >> 4) | (1u << 16); }
 
@@ -211,14 +186,6 @@ __host__ __device__ constexpr uint32_t idesc_e4m3_f32(int n) {
            | (0u << 15) | (0u << 16)              // A, B K-major
            | (static_cast<uint32_t>(n >> 3) << 17)  // N / 8
            | (static_cast<uint32_t>(128 >> 4) << 24);  // M / 16
-}
-
-// Shared-memory matrix descriptor: K-major rows of 128 bytes in the 128-byte swizzle, 8-row groups
-// 1024 bytes apart (tile base 1024-byte aligned).  Advance along K by adding bytes/16 to the low word.
-__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t saddr) {
-    const uint64_t lo = ((saddr & 0x3FFFFu) >> 4) | (1u << 16);
-    const uint64_t hi = (1024u >> 4) | (1u << 14) | (2u << 29);
-    return lo | (hi << 32);
 }
 
 }  // namespace ptx
