@@ -165,6 +165,65 @@ int ovc_attention(const void* q8, const void* k8, const void* v_packed, const fl
                   int64_t repair_rows, void* out, int64_t B, int64_t Sq, int64_t Sk, int64_t H,
                   float softmax_scale, int mid_window_blocks, uint32_t* status, void* stream);
 
+/* ---- VC-Attention baseline: V-Smooth preparation and the mean-restoring attention variant ----
+ *
+ * Replaces the Triton kernels and launches of src/open_vc_attn/_kernels/blackwell/v_smooth.py and the
+ * v_smooth=True specialisation of the attention kernel (cute/flash_fwd_sm100.py:140, 3895-3901,
+ * 4111-4262).  One sequence; Q, K, V bf16 [S,H,128] read in place (no head-major copy).
+ */
+
+/*
+ * labels[h][s] = argmin_k (|c_k|^2 - 2 v_s.c_k), first index on ties (_assign_values, v_smooth.py:10-39).
+ *   v [S,H,128] bf16, centers [H,K,128] bf16, labels [H,S] int32 out; 1 <= K <= min(128, S).
+ * Products are accumulated in float32 by fused multiply-adds over ascending channels; the reference's
+ * BF16 tensor-core product has an unspecified order, so near-tied tokens may be labelled differently.
+ */
+int ovc_vs_assign(const void* v, const void* centers, int32_t* labels, int64_t S, int64_t H, int64_t K, void* stream);
+
+/*
+ * Per-cluster float32 sums [H,K,128] and counts [H,K] of V rows; both outputs are cleared first
+ * (_accumulate_centers, v_smooth.py:42-73, with the torch.zeros of :262-267).
+ */
+int ovc_vs_accumulate(const void* v, const int32_t* labels, float* sums, float* counts, int64_t S, int64_t H, int64_t K,
+                      void* stream);
+
+/* centers = count > 0 ? bf16(sum / count) : centers   (the torch.where of v_smooth.py:281-285). */
+int ovc_vs_update_centers(const float* sums, const float* counts, void* centers, int64_t H, int64_t K, void* stream);
+
+/*
+ * Block means of V in group order and the per-channel maximum of |v - mean| (_block_stats, v_smooth.py:76-94).
+ *   permutation [H,S] int64; means [H,ceil(S/128),128] f32 out; amax [H,128] f32 out (cleared first).
+ * A block's rows are summed in ascending order in float32.
+ */
+int ovc_vs_block_stats(const void* v, const int64_t* permutation, float* means, float* amax, int64_t S, int64_t H,
+                       void* stream);
+
+/*
+ * Permuted FP8 K, FP8 V residual codes, block means in code units and channel scales
+ * (_block_write, v_smooth.py:97-134).
+ *   k_out, codes [S,H,128] fp8; means_out [ceil(S/128),H,128] f32 (BF16-rounded values); scale [H,128] f32.
+ */
+int ovc_vs_block_write(const void* k, const void* v, const int64_t* permutation, const float* means, const float* amax,
+                       void* k_out, void* codes, float* means_out, float* scale, int64_t S, int64_t H, void* stream);
+
+/*
+ * Unscaled saturating cast of f16/bf16 to FP8 (q.to(float8_e4m3fn) in v_smooth.py:161; values beyond the
+ * FP8 range saturate to +-448 here, where torch's cast gives NaN).  elements is a multiple of 8.
+ */
+int ovc_cast_e4m3(const void* x, int dtype, void* out, int64_t elements, void* stream);
+
+/*
+ * ExpCast attention with V-Smooth restoration: as ovc_attention with B = 1, no descales and no repair
+ * prefix, and out = (P~ V_codes + sum over key blocks (row sum of P~ in the block) * means[block]) * scale
+ * / (row sum of P~).
+ *   v_packed      [H,128,Sk_pad] fp8 residual codes (ovc_pack_v of the codes)
+ *   unit_descale  f32, at least H * ceil(max(Sq,Sk)/128) values, all 1.0
+ *   means         [ceil(Sk/128),H,128] f32; channel_scale [H,128] f32
+ */
+int ovc_attention_vsmooth(const void* q8, const void* k8, const void* v_packed, const float* unit_descale,
+                          const float* means, const float* channel_scale, void* out, int64_t Sq, int64_t Sk,
+                          int64_t H, float softmax_scale, int mid_window_blocks, uint32_t* status, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -75,6 +75,8 @@ struct AttnParams {
     const float* k_descale;  // [B,H,n_tiles]
     const float* v_descale;  // [B,H]
     const float* repair_kd;  // [H,repair_rows] or null
+    const float* vs_means;   // V-Smooth: [n_tiles,H,128] block means in code units, else null
+    const float* vs_scale;   // V-Smooth: [H,128] channel scales
     __nv_bfloat16* out;      // [B,Sq,H,128]
     uint32_t* status;
     long long Sq, Sk;
@@ -232,6 +234,10 @@ __device__ __forceinline__ uint32_t bf16x2(float lo, float hi) {
     return r;
 }
 
+// kVS: V-Smooth variant (VC-Attention baseline): V holds residual codes; every key step adds
+// (sum of the tile's probabilities) x (the tile's block mean) to the accumulator, and the output is
+// scaled per channel (cute/flash_fwd_sm100.py:4857-4863 of the reference).
+template <bool kVS>
 __global__ void __launch_bounds__(kThreads, 1)
 attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                  const __grid_constant__ CUtensorMap tmap_v, const AttnParams p) {
@@ -424,6 +430,8 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         const uint32_t my_gate = smem_addr(&sm.gate[stage]);  // "scores copied out, previous probabilities stored"
 
         float row_max = 0.0f, bias = 0.0f, saved_denominator = 0.0f;
+        float l_known = 0.0f;  // V-Smooth: denominator before the previous step's PV, after rescaling
+        int j_prev = 0;        // V-Smooth: key tile of the previous step
         bool ok = true;
         for (int it = 0; it < n_iters; ++it) {
             const int j = tile_at(it, j0, p.first_tile, p.n_tiles);
@@ -508,27 +516,57 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
             }
 #endif
 
-            const bool first_repair = p.first_tile > 0 && j == p.first_tile - 1;
-            const bool rescale = it > 0 && __any_sync(0xFFFFFFFFu, alpha < 1.0f);
-            if (first_repair) {
-                // First repair tile: the denominator holds the original tokens' total only.
-                saved_denominator = __uint_as_float(tmem_ld1(t_o + kDim));
-                tmem_wait_ld();
-            }
-            if (rescale) {
-                // The running max moved: rescale the accumulator and the denominator in place.
-#pragma unroll
-                for (int c = 0; c < 4; ++c) {
-                    uint32_t o[32];
-                    tmem_ld32(t_o + 32 * c, o);
+            if (kVS) {
+                if (it > 0) {
+                    // The previous PV has landed: its tile's probability sum is the growth of the denominator.
+                    // Add that sum times the tile's block mean to the accumulator, then apply this step's rescale.
+                    const float l_cur = __uint_as_float(tmem_ld1(t_o + kDim));
                     tmem_wait_ld();
+                    const float w = l_cur - l_known;
+                    const float4* mean4 = reinterpret_cast<const float4*>(
+                        p.vs_means + (static_cast<long long>(j_prev) * p.H + head) * kDim);
 #pragma unroll
-                    for (int e = 0; e < 32; ++e) o[e] = __float_as_uint(__uint_as_float(o[e]) * alpha);
-                    tmem_st32(t_o + 32 * c, o);
+                    for (int c = 0; c < 4; ++c) {
+                        uint32_t o[32];
+                        tmem_ld32(t_o + 32 * c, o);
+                        tmem_wait_ld();
+#pragma unroll
+                        for (int e = 0; e < 8; ++e) {
+                            const float4 m = __ldg(mean4 + 8 * c + e);
+                            o[4 * e] = __float_as_uint(fmaf(w, m.x, __uint_as_float(o[4 * e])) * alpha);
+                            o[4 * e + 1] = __float_as_uint(fmaf(w, m.y, __uint_as_float(o[4 * e + 1])) * alpha);
+                            o[4 * e + 2] = __float_as_uint(fmaf(w, m.z, __uint_as_float(o[4 * e + 2])) * alpha);
+                            o[4 * e + 3] = __float_as_uint(fmaf(w, m.w, __uint_as_float(o[4 * e + 3])) * alpha);
+                        }
+                        tmem_st32(t_o + 32 * c, o);
+                    }
+                    l_known = l_cur * alpha;
+                    tmem_st1(t_o + kDim, __float_as_uint(l_known));
                 }
-                const float l = __uint_as_float(tmem_ld1(t_o + kDim));
-                tmem_wait_ld();
-                tmem_st1(t_o + kDim, __float_as_uint(l * alpha));
+                j_prev = j;
+            } else {
+                const bool first_repair = p.first_tile > 0 && j == p.first_tile - 1;
+                const bool rescale = it > 0 && __any_sync(0xFFFFFFFFu, alpha < 1.0f);
+                if (first_repair) {
+                    // First repair tile: the denominator holds the original tokens' total only.
+                    saved_denominator = __uint_as_float(tmem_ld1(t_o + kDim));
+                    tmem_wait_ld();
+                }
+                if (rescale) {
+                    // The running max moved: rescale the accumulator and the denominator in place.
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        uint32_t o[32];
+                        tmem_ld32(t_o + 32 * c, o);
+                        tmem_wait_ld();
+#pragma unroll
+                        for (int e = 0; e < 32; ++e) o[e] = __float_as_uint(__uint_as_float(o[e]) * alpha);
+                        tmem_st32(t_o + 32 * c, o);
+                    }
+                    const float l = __uint_as_float(tmem_ld1(t_o + kDim));
+                    tmem_wait_ld();
+                    tmem_st1(t_o + kDim, __float_as_uint(l * alpha));
+                }
             }
             tmem_wait_st();
             if ((warp & 3) == 0) OVC_TL(it, stage * 6 + 5);
@@ -543,11 +581,14 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
             tc_fence_after();
             float l = __uint_as_float(tmem_ld1(t_o + kDim));
             tmem_wait_ld();
+            const float w_last = l - l_known;  // V-Smooth: probability sum of the last tile
             if (p.first_tile > 0) l = saved_denominator;
             const bool bad = l == 0.0f || l != l;
             float inv;
             asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(inv) : "f"(bad ? 1.0f : l));
             const float factor = inv * __ldg(p.v_descale + bh_l);
+            const float* mean_last = kVS ? p.vs_means + (static_cast<long long>(j_prev) * p.H + head) * kDim : nullptr;
+            const float* channel_scale = kVS ? p.vs_scale + static_cast<long long>(head) * kDim : nullptr;
             const long long row = static_cast<long long>(q_tile) * kTile + row_in_tile;
             uint4* dst = reinterpret_cast<uint4*>(p.out + ((static_cast<long long>(batch) * p.Sq + row) * p.H + head) * kDim);
 #pragma unroll
@@ -555,6 +596,12 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
                 uint32_t o[32];
                 tmem_ld32(t_o + 32 * c, o);
                 tmem_wait_ld();
+                if (kVS) {
+#pragma unroll
+                    for (int e = 0; e < 32; ++e)
+                        o[e] = __float_as_uint(fmaf(w_last, __ldg(mean_last + 32 * c + e), __uint_as_float(o[e])) *
+                                               __ldg(channel_scale + 32 * c + e));
+                }
                 if (row < p.Sq) {
 #pragma unroll
                     for (int e = 0; e < 4; ++e) {
@@ -624,10 +671,12 @@ extern "C" int ovc_debug_set_dump(float* buffer) {
 }
 #endif
 
-extern "C" int ovc_attention(const void* q8, const void* k8, const void* v_packed, const float* q_descale,
-                             int64_t q_blocks, const float* k_descale, const float* v_descale, const float* repair_kd,
-                             int64_t repair_rows, void* out, int64_t B, int64_t Sq, int64_t Sk, int64_t H,
-                             float softmax_scale, int mid_window_blocks, uint32_t* status, void* stream) {
+namespace {
+
+int launch_attention(const void* q8, const void* k8, const void* v_packed, const float* q_descale, int64_t q_blocks,
+                     const float* k_descale, const float* v_descale, const float* repair_kd, int64_t repair_rows,
+                     const float* vs_means, const float* vs_scale, void* out, int64_t B, int64_t Sq, int64_t Sk,
+                     int64_t H, float softmax_scale, int mid_window_blocks, uint32_t* status, void* stream) {
     if (!q8 || !k8 || !v_packed || !q_descale || !k_descale || !v_descale || !out || B < 1 || Sq < 1 || Sk < 1 ||
         H < 1 || Sq > (1LL << 30) || Sk > (1LL << 30) || q_blocks < ceil_div(Sq, kTile) || !(softmax_scale > 0.0f) ||
         !isfinite(softmax_scale) || mid_window_blocks < -1 || repair_rows < 0 || repair_rows % kTile != 0 ||
@@ -665,6 +714,7 @@ extern "C" int ovc_attention(const void* q8, const void* k8, const void* v_packe
 
     AttnParams p{};
     p.q_descale = q_descale, p.k_descale = k_descale, p.v_descale = v_descale, p.repair_kd = repair_kd;
+    p.vs_means = vs_means, p.vs_scale = vs_scale;
     p.out = static_cast<__nv_bfloat16*>(out), p.status = status;
     p.Sq = Sq, p.Sk = Sk, p.H = static_cast<int>(H), p.B = static_cast<int>(B);
     p.q_blocks = static_cast<int>(q_blocks), p.n_tiles = static_cast<int>(n_tiles);
@@ -675,11 +725,36 @@ extern "C" int ovc_attention(const void* q8, const void* k8, const void* v_packe
     const size_t smem_bytes = sizeof(SmemLayout) + 1024;
     static bool configured[64] = {};
     if (device < 64 && !configured[device]) {
-        err = cudaFuncSetAttribute(attention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem_bytes));
+        err = cudaFuncSetAttribute(attention_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem_bytes));
+        if (err == cudaSuccess)
+            err = cudaFuncSetAttribute(attention_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem_bytes));
         if (err != cudaSuccess) { set_last_cuda_error(err); return OVC_ERR_CUDA; }
         configured[device] = true;
     }
     const unsigned grid = static_cast<unsigned>(m_blocks * H * B);
-    attention_kernel<<<grid, kThreads, smem_bytes, static_cast<cudaStream_t>(stream)>>>(map_q, map_k, map_v, p);
+    auto s = static_cast<cudaStream_t>(stream);
+    if (vs_means != nullptr) attention_kernel<true><<<grid, kThreads, smem_bytes, s>>>(map_q, map_k, map_v, p);
+    else attention_kernel<false><<<grid, kThreads, smem_bytes, s>>>(map_q, map_k, map_v, p);
     return check_launch();
+}
+
+}  // namespace
+
+extern "C" int ovc_attention(const void* q8, const void* k8, const void* v_packed, const float* q_descale,
+                             int64_t q_blocks, const float* k_descale, const float* v_descale, const float* repair_kd,
+                             int64_t repair_rows, void* out, int64_t B, int64_t Sq, int64_t Sk, int64_t H,
+                             float softmax_scale, int mid_window_blocks, uint32_t* status, void* stream) {
+    return launch_attention(q8, k8, v_packed, q_descale, q_blocks, k_descale, v_descale, repair_kd, repair_rows, nullptr,
+                            nullptr, out, B, Sq, Sk, H, softmax_scale, mid_window_blocks, status, stream);
+}
+
+extern "C" int ovc_attention_vsmooth(const void* q8, const void* k8, const void* v_packed, const float* unit_descale,
+                                     const float* means, const float* channel_scale, void* out, int64_t Sq, int64_t Sk,
+                                     int64_t H, float softmax_scale, int mid_window_blocks, uint32_t* status,
+                                     void* stream) {
+    if (!means || !channel_scale || !unit_descale || !aligned16(means) || !aligned16(channel_scale)) return OVC_ERR_ARGUMENT;
+    const int64_t blocks = ceil_div(Sq > Sk ? Sq : Sk, kTile);
+    // unit_descale: at least H * ceil(max(Sq,Sk)/128) floats equal to 1.0 (no Q/K/V descales on this path).
+    return launch_attention(q8, k8, v_packed, unit_descale, blocks, unit_descale, unit_descale, nullptr, 0, means,
+                            channel_scale, out, 1, Sq, Sk, H, softmax_scale, mid_window_blocks, status, stream);
 }

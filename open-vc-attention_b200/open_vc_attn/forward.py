@@ -68,6 +68,9 @@ def flash_attn_fwd(
     mid_window_blocks=None,
     return_lse=False,
     repair_k_descale=None,
+    v_smooth=False,
+    v_smooth_means=None,
+    v_smooth_scale=None,
     **unsupported,
 ):
     """FP8 ExpCast attention.  Returns (out bf16 in Q's shape, None).
@@ -76,6 +79,9 @@ def flash_attn_fwd(
     [Sk,H,128] view of a [H,128,Sk_pad] buffer.  q_descale [B,H,>=ceil(Sq/128)], k_descale
     [B,H,ceil(Sk/128)], v_descale [B,H], all float32.  cu_seqlens_* / max_seqlen_* are accepted for
     signature compatibility; a 3-D call is one sequence spanning the whole tensor.
+    v_smooth: V holds residual codes of one sequence, ``v_smooth_means`` [1,ceil(Sk/128),H,128] (float32 or
+    bfloat16) the block means in code units and ``v_smooth_scale`` [1,H,128] float32 the channel scales; no
+    descales are taken on that path.
     """
     if unsupported:
         raise NotImplementedError(f"Unsupported kernel options in this build: {sorted(unsupported)}")
@@ -87,6 +93,11 @@ def flash_attn_fwd(
         raise NotImplementedError("return_lse=True is not built")
     if any(t.dtype != torch.float8_e4m3fn for t in (q, k, v)):
         raise ValueError("ExpCast attention expects float8_e4m3fn Q/K/V")
+    if v_smooth:
+        return _v_smooth_forward(q, k, v, v_smooth_means, v_smooth_scale, softmax_scale, mid_window_blocks,
+                                 (q_descale, k_descale, v_descale, repair_k_descale), v_prepacked), None
+    if v_smooth_means is not None or v_smooth_scale is not None:
+        raise ValueError("v_smooth_means / v_smooth_scale need v_smooth=True")
     if q_descale is None or k_descale is None or v_descale is None:
         raise ValueError("ExpCast attention expects q_descale, k_descale and v_descale")
     if v_prepacked:
@@ -168,6 +179,75 @@ def flash_attn_fwd(
         )
         del keep
     return out, None
+
+
+_unit_descales = {}
+
+
+def _unit_descale(device, count):
+    """A device buffer of at least ``count`` ones (the V-Smooth path has no Q/K/V descales)."""
+    key = torch.device(device).index
+    have = _unit_descales.get(key)
+    if have is None or have.numel() < count:
+        have = torch.ones(max(count, 1 << 16), dtype=torch.float32, device=device)
+        _unit_descales[key] = have
+    return have
+
+
+def _v_smooth_forward(q, k, v, means, scale, softmax_scale, mid_window_blocks, descales, v_prepacked):
+    # Argument rules of src/open_vc_attn/_kernels/blackwell/flash_attn/cute/interface.py:560-600 for v_smooth.
+    if any(d is not None for d in descales):
+        raise NotImplementedError("V-Smooth attention takes no descales or repair prefix in this build")
+    if v_prepacked:
+        raise NotImplementedError("V-Smooth attention takes sequence-major V codes")
+    if q.ndim == 4:
+        if q.shape[0] != 1:
+            raise ValueError("V-Smooth attention supports one sequence")
+        q, k, v = q[0], k[0], v[0]
+    if q.ndim != 3 or k.ndim != 3 or q.shape[-1] != 128 or tuple(v.shape) != tuple(k.shape) or k.shape[1] != q.shape[1]:
+        raise ValueError("Expected [S,H,128] Q/K/V with matching heads")
+    sq, heads, _ = q.shape
+    sk = k.shape[0]
+    blocks = (sk + 127) // 128
+    device = q.device
+    if means is None or scale is None:
+        raise ValueError("v_smooth=True needs v_smooth_means and v_smooth_scale")
+    if (
+        means.numel() != blocks * heads * 128
+        or tuple(means.shape[-3:]) != (blocks, heads, 128)
+        or means.device != device
+        or means.dtype not in (torch.float32, torch.bfloat16)
+    ):
+        raise ValueError("v_smooth_means must be [1, key blocks, heads, 128] float32 or bfloat16 on the input device")
+    if scale.numel() != heads * 128 or tuple(scale.shape[-2:]) != (heads, 128) or scale.device != device or scale.dtype != torch.float32:
+        raise ValueError("v_smooth_scale must be float32 [1, heads, 128] on the input device")
+    if softmax_scale is None:
+        softmax_scale = 1.0 / math.sqrt(128)
+    if not math.isfinite(softmax_scale) or softmax_scale <= 0.0:
+        raise ValueError("ExpCast requires a positive finite softmax_scale")
+    window = -1 if mid_window_blocks is None else int(mid_window_blocks)
+    if window < -1:
+        raise ValueError("mid_window_blocks must be None or >= 0")
+    lib = _lib.load()
+    with torch.cuda.device(device):
+        from .quantization import pack_v
+
+        q, k = q.contiguous(), k.contiguous()
+        packed = pack_v(v.contiguous())
+        means = means.float().contiguous()
+        scale = scale.contiguous()
+        ones = _unit_descale(device, heads * ((max(sq, sk) + 127) // 128))
+        out = torch.empty(q.shape, dtype=torch.bfloat16, device=device)
+        _lib.check(
+            lib.ovc_attention_vsmooth(
+                q.data_ptr(), k.data_ptr(), packed.data_ptr(), ones.data_ptr(), means.data_ptr(), scale.data_ptr(),
+                out.data_ptr(), sq, sk, heads, float(softmax_scale), window, status_word(device).data_ptr(),
+                _lib.stream_pointer(device),
+            ),
+            "ovc_attention_vsmooth",
+        )
+        del packed
+    return out
 
 
 _flash_attn_fwd = flash_attn_fwd

@@ -107,6 +107,8 @@ def expcast_attention(
     repair_k_descale=None,
     encoder="packed",
     rows=None,
+    v_smooth_means=None,
+    v_channel_scale=None,
 ):
     """ExpCast attention for one (batch item, head set) on FP8 codes.
 
@@ -114,6 +116,9 @@ def expcast_attention(
     q_descale f32 [H,>=ceil(Sq/128)]; k_descale f32 [H,ceil(Sk/128)]; v_descale f32 [H];
     repair_k_descale f32 [H,R] or None.  ``rows`` optionally restricts the query rows
     computed to a list of 256-row CTA blocks (m_block indices); other rows stay zero.
+    V-Smooth (fwd:4857-4863): v8 holds residual codes, ``v_smooth_means`` f32 [tiles,H,128] the block
+    means in code units and ``v_channel_scale`` f32 [H,128]; each tile adds (sum of its decoded
+    probabilities) x (its block mean) to the accumulator and the result is scaled per channel.
     Returns float32 [Sq,H,128] already rounded to bfloat16 precision.
     """
     sq, h, d = q8.shape
@@ -180,11 +185,16 @@ def expcast_attention(
                     run_max = new_max
                     p = E4M3_DECODE_F32[codes]
                     acc = (acc + p @ vf[c0 : c0 + TILE, head]).astype(F32)
-                    denom = (denom + p.sum(axis=1, dtype=F32)).astype(F32)
+                    tile_sum = p.sum(axis=1, dtype=F32)
+                    if v_smooth_means is not None:
+                        acc = (acc + tile_sum[:, None] * v_smooth_means[tile, head][None, :]).astype(F32)
+                    denom = (denom + tile_sum).astype(F32)
                 if saved is not None:
                     denom = saved
                 bad = (denom == 0) | np.isnan(denom)
                 factor = (F32(1.0) / np.where(bad, F32(1.0), denom)).astype(F32) * F32(v_descale[head])
+                if v_channel_scale is not None:
+                    acc = (acc * v_channel_scale[head][None, :]).astype(F32)
                 out[r0:r1, head] = acc * factor[:, None]
     return _round_bf16(out)
 

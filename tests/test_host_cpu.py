@@ -85,13 +85,19 @@ def test_unbuilt_options_raise_instead_of_degrading():
     with pytest.raises(NotImplementedError, match="return_lse"):
         forward.flash_attn_fwd(q, q, q, return_lse=True, **common)
     with pytest.raises(NotImplementedError, match="Unsupported kernel options"):
+        forward.flash_attn_fwd(q, q, q, v_smooth_head_major=True, **common)
+    with pytest.raises(NotImplementedError, match="takes no descales"):
         forward.flash_attn_fwd(q, q, q, v_smooth=True, **common)
+    with pytest.raises(ValueError, match="needs v_smooth_means"):
+        forward.flash_attn_fwd(q, q, q, v_smooth=True, expcast=True)
+    with pytest.raises(ValueError, match="need v_smooth=True"):
+        forward.flash_attn_fwd(q, q, q, v_smooth_means=d3, **common)
     with pytest.raises(ValueError, match="v_prepacked must use"):
         forward.flash_attn_fwd(q, q, q, v_prepacked=True, **common)
     with pytest.raises(ValueError, match="positive finite softmax_scale"):
         forward.flash_attn_fwd(q, q, q, softmax_scale=0.0, **common)
-    with pytest.raises(NotImplementedError):
-        baselines.vc_attention(q, q, q)
+    with pytest.raises(ValueError, match="same CUDA device"):
+        baselines.vc_attention(q, q, q)  # CPU tensors: the reference's validation message
 
 
 def test_repair_budget_validation(monkeypatch):
