@@ -475,19 +475,14 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
                     s[4 * c + 3] = __float_as_uint(__uint_as_float(s[4 * c + 3]) * f.w);
                 }
             }
-            // Codes against the running max, formed while the row max of this tile is still being
-            // reduced: in the steady state the max does not move and these are the final codes, so
-            // the conversion does not wait for the reduction.  Same formulas either way.
+            // Row max first, then one encoding pass against the (possibly raised) max: a single copy of the
+            // encoder in the loop body measured faster than encoding speculatively while the max is reduced.
             const float code_scale = code_scale0 * kd;
             const uint64_t scale2 = pack2(code_scale, code_scale);
-            uint32_t codes[32];
-            if (it > 0) encode128(s, scale2, pack2(bias, bias), codes);
             const float tile_max = max128(s) * kd;
-
             if ((warp & 3) == 0) OVC_TL(it, stage * 6 + 3);
             float alpha = 1.0f;
-            if (it == 0 || __any_sync(0xFFFFFFFFu, tile_max > row_max)) {
-                // The max moved for some row of the warp (or this is the first tile): new bias, new codes.
+            if (it == 0 || tile_max > row_max) {
                 float new_max = tile_max;
                 alpha = 0.0f;
                 if (it > 0) {
@@ -497,8 +492,9 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
                 }
                 row_max = new_max;
                 bias = expcast_bias(new_max == -INFINITY ? 0.0f : new_max, code_scale0);
-                encode128(s, scale2, pack2(bias, bias), codes);
             }
+            uint32_t codes[32];
+            encode128(s, scale2, pack2(bias, bias), codes);
             if (it > 0) {
                 // The stage's previous PV (step it-1) is issued after this step's QK, so the score
                 // barrier does not cover it: wait for it before P is overwritten or O is rescaled.
