@@ -122,6 +122,31 @@ __device__ __forceinline__ bool wait_bar(SmemLayout& sm, uint64_t* bar, uint32_t
     }
 }
 
+// The MMA warp's reaction time is on the critical path of the shared score buffer, and it shares its
+// scheduler with two conversion warps: descriptors are built before the wait, and after it come only a
+// fence, one election, the four K-steps and the commit.
+__device__ __forceinline__ uint64_t desc64(uint32_t lo) {
+    uint64_t d;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "r"(lo), "r"(ptx::kSmemDescHi));
+    return d;
+}
+__device__ __forceinline__ void qk_issue(uint32_t d_tmem, const uint64_t (&da)[4], const uint64_t (&db)[4], uint32_t idesc,
+                                         uint32_t bar) {
+    asm volatile(
+        "{\n\t.reg .pred leader;\n\t"
+        "tcgen05.fence::after_thread_sync;\n\t"
+        "elect.sync _|leader, 0xFFFFFFFF;\n\t"
+        "@leader tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %5, %9, 0;\n\t"
+        "@leader tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %2, %6, %9, 1;\n\t"
+        "@leader tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %3, %7, %9, 1;\n\t"
+        "@leader tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %4, %8, %9, 1;\n\t"
+        "@leader tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%10];\n\t}"
+        :
+        : "r"(d_tmem), "l"(da[0]), "l"(da[1]), "l"(da[2]), "l"(da[3]), "l"(db[0]), "l"(db[1]), "l"(db[2]), "l"(db[3]),
+          "r"(idesc), "r"(bar)
+        : "memory");
+}
+
 #ifdef OVC_DEBUG_DUMP
 // Debug builds only: raw scores and codes of CTA 0's first key tile go to this buffer.
 __device__ float* g_debug_dump = nullptr;
@@ -300,7 +325,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
     const uint32_t tmem = sm.tmem_base;
 
     if (warp >= 8) {
-        asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
         if (warp == 8) {
             // ---------------- TMA producer ----------------
             if (lane == 0) {
@@ -372,16 +397,17 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
                 [[maybe_unused]] const int it = n;  // step index for debug stamps
                 for (int s = 0; s < 2; ++s) {
                     OVC_TL(it, 12 + s * 6 + 0);
+                    const int qk_step = n + s;  // s = 0 feeds stage 1 step n; s = 1 feeds stage 0 step n + 1
+                    const uint32_t a_lo = smem_desc_lo(smem_addr(sm.q[1 - s]));
+                    const uint32_t b_lo = smem_desc_lo(smem_addr(sm.k[qk_step % kKStages]));
+                    const uint64_t da[4] = {desc64(a_lo), desc64(a_lo + 2), desc64(a_lo + 4), desc64(a_lo + 6)};
+                    const uint64_t db[4] = {desc64(b_lo), desc64(b_lo + 2), desc64(b_lo + 4), desc64(b_lo + 6)};
+                    const uint32_t score_bar = smem_addr(&sm.s_full[1 - s]);
                     ok = __all_sync(0xFFFFFFFFu, wait_bar(sm, &sm.gate[s], n & 1, p.status));
                     if (!ok) break;
-                    tc_fence_after();
                     OVC_TL(it, 12 + s * 6 + 1);
-                    const int qk_step = n + s;  // s = 0 feeds stage 1 step n; s = 1 feeds stage 0 step n + 1
-                    if (qk_step < n_iters) {
-                        mma4_f8_ss(tmem + kColS, smem_desc_lo(smem_addr(sm.q[1 - s])),
-                                   smem_desc_lo(smem_addr(sm.k[qk_step % kKStages])), idesc_qk);
-                        mma_commit_elect(smem_addr(&sm.s_full[1 - s]));
-                    }
+                    if (qk_step < n_iters) qk_issue(tmem + kColS, da, db, idesc_qk, score_bar);
+                    else tc_fence_after();
                     if (n > 0) {
                         mma4_f8_ts(tmem + kColO + s * kColOStride, tmem + kColP + 32 * s,
                                    smem_desc_lo(smem_addr(sm.v[(n - 1) % kVStages])), idesc_pv, n > 1 ? 1u : 0u);
@@ -414,7 +440,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         }
     } else {
         // ---------------- score conversion: one query row per thread ----------------
-        asm volatile("setmaxnreg.inc.sync.aligned.u32 232;");
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 224;");
         const int stage = warp >> 2;
         const int row_in_tile = (warp & 3) * 32 + lane;
         const uint32_t lane_base = tmem + (static_cast<uint32_t>((warp & 3) * 32) << 16);
