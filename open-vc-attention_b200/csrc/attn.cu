@@ -9,20 +9,19 @@
 // through a block of ones appended to the V tile.
 //
 // Warp roles (384 threads): warps 0-3 convert the scores of stage 0 (one query row per thread),
-// warps 4-7 those of stage 1, warp 8 issues TMA loads, warp 9 issues MMAs, warp 10 relays "tile
-// landed" from the TMA barriers into the MMA gate, warp 11 only takes part in register reallocation.
+// warps 4-7 those of stage 1, warp 8 issues TMA loads, warp 9 issues the score products QK^T, warp 10
+// relays "tile landed" from the TMA barriers into the MMA barriers, warp 11 issues the PV products.
 //
-// Schedule.  Issuing an MMA group blocks the issuing thread for about as long as the group runs,
-// and every barrier wait and tcgen05.commit in that thread costs tensor-pipe idle time, so the MMA
-// warp is given the fewest possible of both: one gate per stage and key step.  A conversion thread
-// of stage s arrives on gate[s] once per step, right after it has copied its scores S_s(n) out of
-// tensor memory; by then it has also stored P_s(n-1).  On gate[s] the MMA warp issues
-//     S = Q_{1-s} K^T for the other stage's next step   (the score buffer is free again), commit
-//     O_s += P_s(n-1) [V(n-1) | 1], commit
-// so the other stage's scores are produced while this stage converts, and a stage finds its next
-// scores waiting when it comes back.  The relay adds "K / V tile landed" to the same gates.
-// Shared-memory slots are recycled from progress counters that the conversion warps publish, not
-// from extra commits.
+// Schedule.  The two stages share one score buffer, so the scores form a chain: S_0(n) -> copied out ->
+// S_1(n) -> copied out -> S_0(n+1) ...  Everything on that chain is kept short.  A conversion thread of
+// stage s arrives on gate[s] right after it has copied S_s(n) out of tensor memory; on gate[s] warp 9
+// (descriptors built before the wait) issues S = Q_{1-s} K^T for the other stage and commits to
+// s_full[1-s].  The PV products are off the chain: a conversion thread arrives on p_full[s] when it has
+// stored P_s(n) (and rescaled O_s if the row max moved); warp 11 then issues O_s += P_s(n) [V(n) | 1]
+// and commits to pv_done[s], which the stage waits for before it overwrites P_s one step later.  The
+// relay adds "K(n+1) landed" to gate[1] and "V(n) landed" to p_full[0], the first users of those
+// tiles.  Shared-memory slots are recycled from progress that the conversion warps publish, not from
+// extra commits.
 //
 // Tensor memory map (512 columns): S 0..127 (shared by both stages), P0 128..159, P1 160..191,
 // O0 192..327, O1 328..463; each O region is 128 output columns followed by 8 copies of the
@@ -63,9 +62,10 @@ struct SmemLayout {
     uint64_t k_full[kKStages], v_full[kVStages];
     uint64_t k_empty[kKStages], v_empty[kVStages];  // slot may be refilled (one arrival by a stage-1 thread)
     uint64_t s_full[2];   // scores of a stage are in tensor memory (commit)
-    uint64_t gate[2];     // what the MMA warp waits for before a stage's group
+    uint64_t gate[2];     // the stage has copied its scores out of tensor memory (+ K tile landed for gate[1])
+    uint64_t p_full[2];   // the stage has stored its probabilities of the step (+ V tile landed for p_full[0])
     uint64_t pv_done[2];  // the stage's previous PV has been accumulated (commit)
-    uint64_t o_full[2], drain;
+    uint64_t o_full[2], drain[2];
     uint32_t tmem_base;
     volatile uint32_t abort_flag;
 };
@@ -259,6 +259,13 @@ __device__ __forceinline__ uint32_t bf16x2(float lo, float hi) {
     return r;
 }
 
+// After a failed wait: let the MMAs this thread has issued finish (bounded) before tensor memory is released.
+__device__ __forceinline__ void drain_mmas(SmemLayout& sm, int which) {
+    mma_commit_elect(smem_addr(&sm.drain[which]));
+    const long long t0 = clock64();
+    while (!mbar_try_wait(smem_addr(&sm.drain[which]), 0) && clock64() - t0 < kWaitCycles) {}
+}
+
 // kVS: V-Smooth variant (VC-Attention baseline): V holds residual codes; every key step adds
 // (sum of the tile's probabilities) x (the tile's block mean) to the accumulator, and the output is
 // scaled per channel (cute/flash_fwd_sm100.py:4857-4863 of the reference).
@@ -303,9 +310,12 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
             mbar_init(smem_addr(&sm.v_full[i]), 1);
             mbar_init(smem_addr(&sm.v_empty[i]), 1);
         }
-        mbar_init(smem_addr(&sm.gate[0]), 129);  // 128 conversion threads of the stage + the relay
-        mbar_init(smem_addr(&sm.gate[1]), 129);
-        mbar_init(smem_addr(&sm.drain), 1);
+        mbar_init(smem_addr(&sm.gate[0]), 128);    // the stage's conversion threads
+        mbar_init(smem_addr(&sm.gate[1]), 129);    // + the relay: K(n+1) has landed
+        mbar_init(smem_addr(&sm.p_full[0]), 129);  // + the relay: V(n) has landed
+        mbar_init(smem_addr(&sm.p_full[1]), 128);
+        mbar_init(smem_addr(&sm.drain[0]), 1);
+        mbar_init(smem_addr(&sm.drain[1]), 1);
         sm.abort_flag = 0;
         mbar_init_fence();
     }
@@ -383,7 +393,6 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         } else if (warp == 9) {
             // ---------------- MMA issuer ----------------
             constexpr uint32_t idesc_qk = idesc_e4m3_f32(kTile);
-            constexpr uint32_t idesc_pv = idesc_e4m3_f32(kPvN);
             bool ok = wait_bar(sm, &sm.q_full[0], 0, p.status) && wait_bar(sm, &sm.q_full[1], 0, p.status) &&
                       wait_bar(sm, &sm.k_full[0], 0, p.status);
             ok = __all_sync(0xFFFFFFFFu, ok);
@@ -391,13 +400,14 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
                 mma4_f8_ss(tmem + kColS, smem_desc_lo(smem_addr(sm.q[0])), smem_desc_lo(smem_addr(sm.k[0])), idesc_qk);
                 mma_commit_elect(smem_addr(&sm.s_full[0]));
             }
-            // gate[s] completion n: stage s has copied S_s(n) out (n < N) and stored P_s(n-1) (n > 0).
-            // Then: scores of the other stage's next step (stage 1: step n, stage 0: step n+1), PV_s(n-1).
-            for (int n = 0; ok && n <= n_iters; ++n) {
+            // gate[s] completion n: stage s has copied S_s(n) out, so the score buffer is free for the other
+            // stage's next step (stage 1: step n, stage 0: step n + 1).
+            for (int n = 0; ok && n < n_iters; ++n) {
                 [[maybe_unused]] const int it = n;  // step index for debug stamps
                 for (int s = 0; s < 2; ++s) {
                     OVC_TL(it, 12 + s * 6 + 0);
-                    const int qk_step = n + s;  // s = 0 feeds stage 1 step n; s = 1 feeds stage 0 step n + 1
+                    const int qk_step = n + s;
+                    if (qk_step >= n_iters) break;
                     const uint32_t a_lo = smem_desc_lo(smem_addr(sm.q[1 - s]));
                     const uint32_t b_lo = smem_desc_lo(smem_addr(sm.k[qk_step % kKStages]));
                     const uint64_t da[4] = {desc64(a_lo), desc64(a_lo + 2), desc64(a_lo + 4), desc64(a_lo + 6)};
@@ -406,35 +416,41 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
                     ok = __all_sync(0xFFFFFFFFu, wait_bar(sm, &sm.gate[s], n & 1, p.status));
                     if (!ok) break;
                     OVC_TL(it, 12 + s * 6 + 1);
-                    if (qk_step < n_iters) qk_issue(tmem + kColS, da, db, idesc_qk, score_bar);
-                    else tc_fence_after();
-                    if (n > 0) {
-                        mma4_f8_ts(tmem + kColO + s * kColOStride, tmem + kColP + 32 * s,
-                                   smem_desc_lo(smem_addr(sm.v[(n - 1) % kVStages])), idesc_pv, n > 1 ? 1u : 0u);
-                        mma_commit_elect(smem_addr(n < n_iters ? &sm.pv_done[s] : &sm.o_full[s]));
-                    }
+                    qk_issue(tmem + kColS, da, db, idesc_qk, score_bar);
                     OVC_TL(it, 12 + s * 6 + 2);
                 }
             }
-            if (!ok) {
-                // Let MMAs already issued finish before tensor memory is released.
-                mma_commit_elect(smem_addr(&sm.drain));
-                const long long t0 = clock64();
-                while (!mbar_try_wait(smem_addr(&sm.drain), 0) && clock64() - t0 < kWaitCycles) {}
+            if (!ok) drain_mmas(sm, 0);
+        } else if (warp == 11) {
+            // ---------------- PV issuer ----------------
+            // p_full[s] completion n: stage s has stored P_s(n) and V(n) has landed.
+            constexpr uint32_t idesc_pv = idesc_e4m3_f32(kPvN);
+            bool ok = true;
+            for (int n = 0; ok && n < n_iters; ++n) {
+                for (int s = 0; s < 2; ++s) {
+                    ok = __all_sync(0xFFFFFFFFu, wait_bar(sm, &sm.p_full[s], n & 1, p.status));
+                    if (!ok) break;
+                    tc_fence_after();
+                    mma4_f8_ts(tmem + kColO + s * kColOStride, tmem + kColP + 32 * s,
+                               smem_desc_lo(smem_addr(sm.v[n % kVStages])), idesc_pv, n > 0 ? 1u : 0u);
+                    mma_commit_elect(smem_addr(n + 1 < n_iters ? &sm.pv_done[s] : &sm.o_full[s]));
+                }
             }
+            if (!ok) drain_mmas(sm, 1);
         } else if (warp == 10) {
-            // ---------------- relay: TMA arrivals -> gates ----------------
-            // gate[0] completion n precedes PV with V(n-1); gate[1] completion n precedes QK with K(n+1).
+            // ---------------- relay: TMA arrivals -> MMA barriers ----------------
+            // gate[1] completion n precedes the first product with K(n+1); p_full[0] completion n the first
+            // with V(n).  One arrival per phase: the previous phase must have completed first.
             if (lane == 0) {
-                for (int n = 0; n <= n_iters; ++n) {
-                    if (n > 0 && !wait_bar(sm, &sm.v_full[(n - 1) % kVStages], ((n - 1) / kVStages) & 1, p.status)) break;
-                    if (n > 0 && !wait_bar(sm, &sm.gate[0], (n - 1) & 1, p.status)) break;
-                    mbar_arrive(smem_addr(&sm.gate[0]));
+                for (int n = 0; n < n_iters; ++n) {
+                    if (n > 0 && !wait_bar(sm, &sm.gate[1], (n - 1) & 1, p.status)) break;
                     if (n + 1 < n_iters &&
                         !wait_bar(sm, &sm.k_full[(n + 1) % kKStages], ((n + 1) / kKStages) & 1, p.status))
                         break;
-                    if (n > 0 && !wait_bar(sm, &sm.gate[1], (n - 1) & 1, p.status)) break;
                     mbar_arrive(smem_addr(&sm.gate[1]));
+                    if (n > 0 && !wait_bar(sm, &sm.p_full[0], (n - 1) & 1, p.status)) break;
+                    if (!wait_bar(sm, &sm.v_full[n % kVStages], (n / kVStages) & 1, p.status)) break;
+                    mbar_arrive(smem_addr(&sm.p_full[0]));
                 }
             }
         }
@@ -453,7 +469,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         const float code_scale0 = sigma * 4.76837158203125e-07f;  // sigma * 8 * 2^-24
         const float* kd_row = p.k_descale + bh_l * p.n_tiles;
         const int tail_valid = static_cast<int>(p.Sk - static_cast<long long>(p.n_tiles - 1) * kTile);
-        const uint32_t my_gate = smem_addr(&sm.gate[stage]);  // "scores copied out, previous probabilities stored"
+        const uint32_t my_gate = smem_addr(&sm.gate[stage]);  // "scores copied out"
 
         float row_max = 0.0f, bias = 0.0f, saved_denominator = 0.0f;
         float l_known = 0.0f;  // V-Smooth: denominator before the previous step's PV, after rescaling
@@ -522,8 +538,8 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
             uint32_t codes[32];
             encode128(s, scale2, pack2(bias, bias), codes);
             if (it > 0) {
-                // The stage's previous PV (step it-1) is issued after this step's QK, so the score
-                // barrier does not cover it: wait for it before P is overwritten or O is rescaled.
+                // The stage's previous PV (step it-1) reads P_s and accumulates into O_s: wait for it before
+                // P is overwritten or O is rescaled.
                 ok = __all_sync(0xFFFFFFFFu, wait_bar(sm, &sm.pv_done[stage], (it - 1) & 1, p.status));
                 if (!ok) break;
                 tc_fence_after();
@@ -591,12 +607,9 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
                 }
             }
             tmem_wait_st();
-            if ((warp & 3) == 0) OVC_TL(it, stage * 6 + 5);
-        }
-        // The last probabilities are stored; there are no further scores to copy out.
-        if (ok) {
             tc_fence_before();
-            mbar_arrive(my_gate);
+            mbar_arrive(smem_addr(&sm.p_full[stage]));  // P_s(it) stored, O_s rescaled
+            if ((warp & 3) == 0) OVC_TL(it, stage * 6 + 5);
         }
         if (ok) ok = __all_sync(0xFFFFFFFFu, wait_bar(sm, &sm.o_full[stage], 0, p.status));
         if (ok) {
