@@ -193,3 +193,81 @@ def test_diffusion_adapter_argument_policy(monkeypatch):
     monkeypatch.setenv("OPEN_VC_ATTN_MODE", "bf16")
     with pytest.raises(ValueError, match="reference with bf16"):
         DenseDiffusionAdapter(2, 128, 0.1)
+
+
+def test_benchmark_statistics_and_shapes():
+    # tests/cpu/test_records.py of the reference checks the same helpers through its record validator
+    from open_vc_attn.benchmarking import measurement
+
+    summary = measurement.summarize([2.0, 1.0, 3.0])
+    assert summary["median_ms"] == 2.0 and summary["min_ms"] == 1.0 and summary["max_ms"] == 3.0
+    assert summary["samples_ms"] == [2.0, 1.0, 3.0] and abs(summary["cv_percent"] - 40.8248) < 1e-3
+    paired = measurement.speedup([4.0, 2.0, 6.0], [2.0, 2.0, 2.0])
+    assert paired["ratio_of_medians"] == 2.0 and paired["median_paired_ratio"] == 2.0
+    assert paired["paired_ratios"] == [2.0, 1.0, 3.0] and paired["latency_reduction_percent"] == 50.0
+    for bad in ([], [1.0, float("nan")], [0.0], [-1.0]):
+        with pytest.raises(ValueError, match="finite and positive"):
+            measurement.summarize(bad)
+    with pytest.raises(ValueError, match="equal nonzero length"):
+        measurement.speedup([1.0], [1.0, 2.0])
+    assert measurement.parse_shape("73397x56x128") == (73397, 56, 128)
+    assert measurement.parse_shape("1024,7,128") == (1024, 7, 128)
+    for bad in ("1024x7", "1024x7x64", "0x7x128", "axbx128"):
+        with pytest.raises(ValueError, match="SxHx128"):
+            measurement.parse_shape(bad)
+
+
+def _record(rounds=2, isolated=True):
+    timing = lambda values: {"samples_ms": values}  # noqa: E731
+    return {
+        "schema_version": 1, "status": "complete", "baseline": "bf16", "scope": "attention", "timing": "events",
+        "gpu": "B200", "isolation_checked": isolated, "settings": {"rounds": rounds, "repair_budget": 0.0, "preparation": "auto"},
+        "shapes": [{
+            "shape": [1024, 7, 128],
+            "timings": {"bf16": timing([2.0, 2.0]), "vc": timing([1.5, 1.5]), "open-vc": timing([1.0, 1.0])},
+            "accuracy": {"open-vc": {"finite": True, "relative_l2": 0.03}, "vc": {"finite": True, "relative_l2": 0.031}},
+        }],
+    }
+
+
+def test_benchmark_report_rendering():
+    from open_vc_attn.benchmarking import report
+
+    text = report.render(_record())
+    assert "| 1024 x 7 x 128 | 2.000 | 1.500 | 1.000 | 2.000x | 3.000% |" in text
+    assert "Shared-GPU" not in text and "Shared-GPU result" in report.render(_record(isolated=False))
+    assert "| 1.333x |" in report.render(_record(), candidate="vc")
+    with pytest.raises(ValueError, match="complete standalone benchmark report"):
+        report.render({**_record(), "status": "running"})
+    with pytest.raises(ValueError, match="Incomplete sample count"):
+        report.render(_record(rounds=3))
+    broken = _record()
+    broken["shapes"][0]["accuracy"]["open-vc"]["finite"] = False
+    with pytest.raises(ValueError, match="finite output"):
+        report.render(broken)
+    with pytest.raises(ValueError, match="must be measured backends"):
+        report.render(_record(), baseline="fa3")
+
+
+def test_benchmark_command_line_rules(capsys):
+    from open_vc_attn.benchmarking import runner
+
+    parser = runner.build_parser()
+    assert runner.validated_shapes(parser.parse_args(["--preset", "smoke"]), parser) == [(129, 2, 128), (1024, 7, 128)]
+    assert len(runner.validated_shapes(parser.parse_args(["--preset", "video"]), parser)) == 6
+    for argv, message in (
+        (["--rounds", "0"], "Rounds/repeats must be positive"),
+        (["--backends", "bf16", "bf16"], "Duplicate backend names"),
+        (["--backends", "vc", "open-vc"], "baseline must be included"),
+        (["--repair-budget", "1.0"], "in \\[0, 1\\)"),
+        (["--repair-budget", "0.01", "--backends", "bf16", "vc"], "requires the open-vc backend"),
+        (["--preparation", "fused"], "requires quantize-attention scope"),
+        (["--repair-budget", "0.01", "--shapes", "4096x7x128"], "sequence lengths >= 32768"),
+        (["--shapes", "64x2x128"], "vc backend requires sequence lengths >= 128"),
+        (["--shapes", "64x2x64"], "SxHx128"),
+    ):
+        with pytest.raises(SystemExit):
+            runner.validated_shapes(parser.parse_args(argv), parser)
+        import re
+
+        assert re.search(message, capsys.readouterr().err)
