@@ -78,6 +78,7 @@ struct AttnParams {
     const float* vs_means;   // V-Smooth: [n_tiles,H,128] block means in code units, else null
     const float* vs_scale;   // V-Smooth: [H,128] channel scales
     __nv_bfloat16* out;      // [B,Sq,H,128]
+    float* lse;              // [B,H,Sq] log-sum-exp of the scaled scores, or null
     uint32_t* status;
     long long Sq, Sk;
     int H, B, q_blocks, n_tiles, first_tile, m_blocks, mid_window;
@@ -622,6 +623,13 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
             float inv;
             asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(inv) : "f"(bad ? 1.0f : l));
             const float factor = inv * __ldg(p.v_descale + bh_l);
+            if (p.lse != nullptr && static_cast<long long>(q_tile) * kTile + row_in_tile < p.Sq) {
+                // (m*sigma + log2(l) - 8) ln 2: the codes put the row maximum at 2^8 (cute/flash_fwd_sm100.py:4455-4466).
+                float lg;
+                asm("lg2.approx.ftz.f32 %0, %1;" : "=f"(lg) : "f"(l));
+                p.lse[bh_l * p.Sq + static_cast<long long>(q_tile) * kTile + row_in_tile] =
+                    bad ? -INFINITY : (fmaf(row_max, sigma, lg) - 8.0f) * 0.6931471805599453f;
+            }
             const float* mean_last = kVS ? p.vs_means + (static_cast<long long>(j_prev) * p.H + head) * kDim : nullptr;
             const float* channel_scale = kVS ? p.vs_scale + static_cast<long long>(head) * kDim : nullptr;
             const long long row = static_cast<long long>(q_tile) * kTile + row_in_tile;
@@ -710,8 +718,8 @@ namespace {
 
 int launch_attention(const void* q8, const void* k8, const void* v_packed, const float* q_descale, int64_t q_blocks,
                      const float* k_descale, const float* v_descale, const float* repair_kd, int64_t repair_rows,
-                     const float* vs_means, const float* vs_scale, void* out, int64_t B, int64_t Sq, int64_t Sk,
-                     int64_t H, float softmax_scale, int mid_window_blocks, uint32_t* status, void* stream) {
+                     const float* vs_means, const float* vs_scale, void* out, float* lse, int64_t B, int64_t Sq,
+                     int64_t Sk, int64_t H, float softmax_scale, int mid_window_blocks, uint32_t* status, void* stream) {
     if (!q8 || !k8 || !v_packed || !q_descale || !k_descale || !v_descale || !out || B < 1 || Sq < 1 || Sk < 1 ||
         H < 1 || Sq > (1LL << 30) || Sk > (1LL << 30) || q_blocks < ceil_div(Sq, kTile) || !(softmax_scale > 0.0f) ||
         !isfinite(softmax_scale) || mid_window_blocks < -1 || repair_rows < 0 || repair_rows % kTile != 0 ||
@@ -750,7 +758,7 @@ int launch_attention(const void* q8, const void* k8, const void* v_packed, const
     AttnParams p{};
     p.q_descale = q_descale, p.k_descale = k_descale, p.v_descale = v_descale, p.repair_kd = repair_kd;
     p.vs_means = vs_means, p.vs_scale = vs_scale;
-    p.out = static_cast<__nv_bfloat16*>(out), p.status = status;
+    p.out = static_cast<__nv_bfloat16*>(out), p.lse = lse, p.status = status;
     p.Sq = Sq, p.Sk = Sk, p.H = static_cast<int>(H), p.B = static_cast<int>(B);
     p.q_blocks = static_cast<int>(q_blocks), p.n_tiles = static_cast<int>(n_tiles);
     p.first_tile = static_cast<int>(repair_rows / kTile), p.m_blocks = static_cast<int>(m_blocks);
@@ -780,7 +788,16 @@ extern "C" int ovc_attention(const void* q8, const void* k8, const void* v_packe
                              int64_t repair_rows, void* out, int64_t B, int64_t Sq, int64_t Sk, int64_t H,
                              float softmax_scale, int mid_window_blocks, uint32_t* status, void* stream) {
     return launch_attention(q8, k8, v_packed, q_descale, q_blocks, k_descale, v_descale, repair_kd, repair_rows, nullptr,
-                            nullptr, out, B, Sq, Sk, H, softmax_scale, mid_window_blocks, status, stream);
+                            nullptr, out, nullptr, B, Sq, Sk, H, softmax_scale, mid_window_blocks, status, stream);
+}
+
+extern "C" int ovc_attention_lse(const void* q8, const void* k8, const void* v_packed, const float* q_descale,
+                                 int64_t q_blocks, const float* k_descale, const float* v_descale, const float* repair_kd,
+                                 int64_t repair_rows, void* out, float* lse, int64_t B, int64_t Sq, int64_t Sk, int64_t H,
+                                 float softmax_scale, int mid_window_blocks, uint32_t* status, void* stream) {
+    if (lse == nullptr) return OVC_ERR_ARGUMENT;
+    return launch_attention(q8, k8, v_packed, q_descale, q_blocks, k_descale, v_descale, repair_kd, repair_rows, nullptr,
+                            nullptr, out, lse, B, Sq, Sk, H, softmax_scale, mid_window_blocks, status, stream);
 }
 
 extern "C" int ovc_attention_vsmooth(const void* q8, const void* k8, const void* v_packed, const float* unit_descale,
@@ -791,5 +808,5 @@ extern "C" int ovc_attention_vsmooth(const void* q8, const void* k8, const void*
     const int64_t blocks = ceil_div(Sq > Sk ? Sq : Sk, kTile);
     // unit_descale: at least H * ceil(max(Sq,Sk)/128) floats equal to 1.0 (no Q/K/V descales on this path).
     return launch_attention(q8, k8, v_packed, unit_descale, blocks, unit_descale, unit_descale, nullptr, 0, means,
-                            channel_scale, out, 1, Sq, Sk, H, softmax_scale, mid_window_blocks, status, stream);
+                            channel_scale, out, nullptr, 1, Sq, Sk, H, softmax_scale, mid_window_blocks, status, stream);
 }

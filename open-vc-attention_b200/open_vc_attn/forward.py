@@ -73,7 +73,10 @@ def flash_attn_fwd(
     v_smooth_scale=None,
     **unsupported,
 ):
-    """FP8 ExpCast attention.  Returns (out bf16 in Q's shape, None).
+    """FP8 ExpCast attention.  Returns (out bf16 in Q's shape, lse or None).
+
+    With ``return_lse`` the second value is the float32 log-sum-exp of the scaled scores, [B,H,Sq] for 4-D and
+    [H,Sq] for 3-D inputs (the shapes of cute/interface.py:410 of the reference).
 
     q [Sq,H,128] or [B,Sq,H,128] e4m3; k the same with Sk; v like k, or (v_prepacked) the logical
     [Sk,H,128] view of a [H,128,Sk_pad] buffer.  q_descale [B,H,>=ceil(Sq/128)], k_descale
@@ -89,8 +92,6 @@ def flash_attn_fwd(
         raise NotImplementedError("Only the ExpCast FP8 path (expcast=True) is built")
     if causal:
         raise NotImplementedError("causal=True is not built; this engine is dense non-causal attention")
-    if return_lse:
-        raise NotImplementedError("return_lse=True is not built")
     if any(t.dtype != torch.float8_e4m3fn for t in (q, k, v)):
         raise ValueError("ExpCast attention expects float8_e4m3fn Q/K/V")
     if v_smooth:
@@ -167,18 +168,28 @@ def flash_attn_fwd(
             packed_ptr = keep.data_ptr()
         out = torch.empty(q.shape, dtype=torch.bfloat16, device=device)
         q_descale, k_descale, v_descale = q_descale.contiguous(), k_descale.contiguous(), v_descale.contiguous()
-        _lib.check(
-            lib.ovc_attention(
-                q.data_ptr(), k.data_ptr(), packed_ptr, q_descale.data_ptr(), q_descale.shape[2],
-                k_descale.data_ptr(), v_descale.data_ptr(),
-                None if repair_k_descale is None else repair_k_descale.data_ptr(), repair_rows,
-                out.data_ptr(), batch, sq, sk, heads, float(softmax_scale), window,
-                status_word(device).data_ptr(), _lib.stream_pointer(device),
-            ),
-            "ovc_attention",
-        )
+        repair_ptr = None if repair_k_descale is None else repair_k_descale.data_ptr()
+        tail = (batch, sq, sk, heads, float(softmax_scale), window, status_word(device).data_ptr(), _lib.stream_pointer(device))
+        lse = None
+        if return_lse:
+            lse = torch.empty((batch, heads, sq) if q.ndim == 4 else (heads, sq), dtype=torch.float32, device=device)
+            _lib.check(
+                lib.ovc_attention_lse(
+                    q.data_ptr(), k.data_ptr(), packed_ptr, q_descale.data_ptr(), q_descale.shape[2], k_descale.data_ptr(),
+                    v_descale.data_ptr(), repair_ptr, repair_rows, out.data_ptr(), lse.data_ptr(), *tail,
+                ),
+                "ovc_attention_lse",
+            )
+        else:
+            _lib.check(
+                lib.ovc_attention(
+                    q.data_ptr(), k.data_ptr(), packed_ptr, q_descale.data_ptr(), q_descale.shape[2], k_descale.data_ptr(),
+                    v_descale.data_ptr(), repair_ptr, repair_rows, out.data_ptr(), *tail,
+                ),
+                "ovc_attention",
+            )
         del keep
-    return out, None
+    return out, lse
 
 
 _unit_descales = {}

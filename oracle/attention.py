@@ -109,6 +109,7 @@ def expcast_attention(
     rows=None,
     v_smooth_means=None,
     v_channel_scale=None,
+    return_lse=False,
 ):
     """ExpCast attention for one (batch item, head set) on FP8 codes.
 
@@ -119,7 +120,8 @@ def expcast_attention(
     V-Smooth (fwd:4857-4863): v8 holds residual codes, ``v_smooth_means`` f32 [tiles,H,128] the block
     means in code units and ``v_channel_scale`` f32 [H,128]; each tile adds (sum of its decoded
     probabilities) x (its block mean) to the accumulator and the result is scaled per channel.
-    Returns float32 [Sq,H,128] already rounded to bfloat16 precision.
+    Returns float32 [Sq,H,128] already rounded to bfloat16 precision; with ``return_lse`` also the float32
+    log-sum-exp [H,Sq] = (m*sigma + log2(l) - 8) ln 2, -inf where l is 0 or NaN (fwd:4437-4475).
     """
     sq, h, d = q8.shape
     sk = k8.shape[0]
@@ -137,6 +139,7 @@ def expcast_attention(
     vf = np.zeros((n_tiles * TILE, h, d), dtype=F32)
     vf[:sk] = e4m3_decode(v8)
     out = np.zeros((sq, h, d), dtype=F32)
+    lse = np.zeros((h, sq), dtype=F32)
     m_blocks = (sq + 2 * TILE - 1) // (2 * TILE)
     todo = range(m_blocks) if rows is None else rows
     q_blocks = q_descale.shape[-1]
@@ -196,6 +199,11 @@ def expcast_attention(
                 if v_channel_scale is not None:
                     acc = (acc * v_channel_scale[head][None, :]).astype(F32)
                 out[r0:r1, head] = acc * factor[:, None]
+                with np.errstate(divide="ignore", invalid="ignore"):
+                    value = ((run_max * sigma + np.log2(np.where(bad, F32(1.0), denom)).astype(F32)).astype(F32) - F32(8.0)) * F32(math.log(2.0))
+                lse[head, r0:r1] = np.where(bad, F32(-np.inf), value)
+    if return_lse:
+        return _round_bf16(out), lse
     return _round_bf16(out)
 
 

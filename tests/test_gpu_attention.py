@@ -122,8 +122,6 @@ def test_validation_errors():
         ovc.attention(q.clone().requires_grad_(), q, q)
     with pytest.raises(NotImplementedError, match="causal"):
         ovc.attention(q, q, q, causal=True)
-    with pytest.raises(NotImplementedError, match="return_lse"):
-        ovc.attention(q, q, q, return_lse=True)
     with pytest.raises(ValueError, match="not available"):
         ovc.attention(q, q, q, mode="bf16", version="reference")
     prepared = api.prepare_fp8(q, q, q)
@@ -218,3 +216,31 @@ def test_diffusion_adapter_packed_sequences_and_padding(monkeypatch):
     assert torch.equal(out[:129], impl.forward(q[:129], k[:129], v[:129]))
     with pytest.raises(ValueError):
         impl.forward_varlen(q, k, v, cu_seqlens=cu, max_seqlen=129)
+
+
+@pytest.mark.parametrize("shape", [(300, 2), (2, 700, 3)])
+def test_log_sum_exp_output(shape):
+    """return_lse=True: against the oracle's formula and against the exact log-sum-exp of the scaled scores."""
+    ovc, api, forward = _api()
+    torch.manual_seed(11)
+    q, k, v = [torch.randn(*shape, 128, device=DEV, dtype=torch.bfloat16) for _ in range(3)]
+    out, lse = ovc.attention(q, k, v, return_lse=True)
+    forward.check_status(q.device)
+    assert torch.equal(out, ovc.attention(q, k, v))  # the output does not depend on the option
+    batched = len(shape) == 3
+    heads, rows = shape[-1], shape[-2]
+    assert lse.dtype == torch.float32 and tuple(lse.shape) == ((shape[0], heads, rows) if batched else (heads, rows))
+    qf, kf = f32(q), f32(k)
+    for b in range(shape[0] if batched else 1):
+        qb, kb, vb = (f32(t)[b] if batched else f32(t) for t in (q, k, v))
+        pq, pk, pv = oprep.quantize_per_block(qb[None]), oprep.quantize_per_block(kb[None]), oprep.quantize_per_head(vb[None])
+        _, want = oatt.expcast_attention(pq[0][0], pk[0][0], pv[0][0], pq[1][0], pk[1][0], pv[1][0], return_lse=True)
+        got = f32(lse)[b] if batched else f32(lse)
+        assert np.abs(got - want).max() < 2e-3
+        scores = np.einsum("qhd,khd->hqk", qb.astype(np.float64), kb.astype(np.float64)) / np.sqrt(128.0)
+        exact = np.log(np.exp(scores - scores.max(axis=-1, keepdims=True)).sum(axis=-1)) + scores.max(axis=-1)
+        assert np.abs(got - exact).max() < 0.1
+    if not batched:
+        long_q = torch.randn(32768, 1, 128, device=DEV, dtype=torch.bfloat16)
+        with pytest.raises(ValueError, match="without LSE"):  # src/open_vc_attn/api.py:152-153 of the reference
+            api.attention_fp8(api.prepare_fp8_fused(long_q, long_q, long_q), return_lse=True)

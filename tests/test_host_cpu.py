@@ -82,8 +82,6 @@ def test_unbuilt_options_raise_instead_of_degrading():
     common = dict(q_descale=d3, k_descale=d3, v_descale=d2, expcast=True)
     with pytest.raises(NotImplementedError, match="causal"):
         forward.flash_attn_fwd(q, q, q, causal=True, **common)
-    with pytest.raises(NotImplementedError, match="return_lse"):
-        forward.flash_attn_fwd(q, q, q, return_lse=True, **common)
     with pytest.raises(NotImplementedError, match="Unsupported kernel options"):
         forward.flash_attn_fwd(q, q, q, v_smooth_head_major=True, **common)
     with pytest.raises(NotImplementedError, match="takes no descales"):

@@ -46,3 +46,16 @@ def test_prepared_tensors_reconstruct_v_and_attention_stays_close():
         v_smooth_means=prepared["means"], v_channel_scale=prepared["scale"],
     )
     assert oatt.relative_l2(out, oatt.exact_attention(q, k, v)) < 0.10
+
+
+def test_log_sum_exp_of_the_restatement_tracks_the_exact_value():
+    from oracle import prep as oprep
+
+    rng = np.random.default_rng(3)
+    q, k, v = [rng.normal(size=(200, 2, 128)).astype(np.float32) for _ in range(3)]
+    pq, pk, pv = oprep.quantize_per_block(q[None]), oprep.quantize_per_block(k[None]), oprep.quantize_per_head(v[None])
+    out, lse = oatt.expcast_attention(pq[0][0], pk[0][0], pv[0][0], pq[1][0], pk[1][0], pv[1][0], return_lse=True)
+    assert lse.shape == (2, 200) and lse.dtype == np.float32
+    scores = np.einsum("qhd,khd->hqk", q.astype(np.float64), k.astype(np.float64)) / np.sqrt(128.0)
+    exact = np.log(np.exp(scores - scores.max(axis=-1, keepdims=True)).sum(axis=-1)) + scores.max(axis=-1)
+    assert np.abs(lse - exact).max() < 0.1
