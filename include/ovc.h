@@ -166,15 +166,19 @@ int ovc_attention(const void* q8, const void* k8, const void* v_packed, const fl
                   float softmax_scale, int mid_window_blocks, uint32_t* status, void* stream);
 
 /*
- * ovc_attention that also writes the log-sum-exp of the scaled scores of every query row (return_lse=True
- * of _flash_attn_fwd, cute/interface.py:139-143 and cute/flash_fwd_sm100.py:4437-4475):
- *   lse [B,H,Sq] f32 = (m * sigma + log2(l) - 8) * ln 2 with m the row maximum of the descaled scores,
- *   sigma = softmax_scale * log2(e) * q_descale and l the denominator; -inf for a row whose l is 0 or NaN.
+ * ovc_attention with the two options of _flash_attn_fwd that the default call does not use
+ * (cute/interface.py:122,139-143):
+ *   lse     [B,H,Sq] f32 or NULL: log-sum-exp of the scaled scores of every query row,
+ *           (m * sigma + log2(l) - 8) * ln 2 with m the row maximum of the descaled scores,
+ *           sigma = softmax_scale * log2(e) * q_descale and l the denominator; -inf for a row whose l is 0 or NaN
+ *           (cute/flash_fwd_sm100.py:4437-4475).
+ *   causal  non-zero: key column c is visible to query row r iff c < r + 1 + Sk - Sq (cute/mask.py:186-199);
+ *           tiles wholly above the diagonal are skipped.  Needs mid_window_blocks = -1 and no repair prefix.
  */
-int ovc_attention_lse(const void* q8, const void* k8, const void* v_packed, const float* q_descale,
-                      int64_t q_blocks, const float* k_descale, const float* v_descale, const float* repair_kd,
-                      int64_t repair_rows, void* out, float* lse, int64_t B, int64_t Sq, int64_t Sk, int64_t H,
-                      float softmax_scale, int mid_window_blocks, uint32_t* status, void* stream);
+int ovc_attention_ex(const void* q8, const void* k8, const void* v_packed, const float* q_descale,
+                     int64_t q_blocks, const float* k_descale, const float* v_descale, const float* repair_kd,
+                     int64_t repair_rows, void* out, float* lse, int causal, int64_t B, int64_t Sq, int64_t Sk,
+                     int64_t H, float softmax_scale, int mid_window_blocks, uint32_t* status, void* stream);
 
 /* ---- VC-Attention baseline: V-Smooth preparation and the mean-restoring attention variant ----
  *

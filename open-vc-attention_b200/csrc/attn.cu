@@ -270,7 +270,7 @@ __device__ __forceinline__ void drain_mmas(SmemLayout& sm, int which) {
 // kVS: V-Smooth variant (VC-Attention baseline): V holds residual codes; every key step adds
 // (sum of the tile's probabilities) x (the tile's block mean) to the accumulator, and the output is
 // scaled per channel (cute/flash_fwd_sm100.py:4857-4863 of the reference).
-template <bool kVS>
+template <bool kVS, bool kCausal>
 __global__ void __launch_bounds__(kThreads, 1)
 attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                  const __grid_constant__ CUtensorMap tmap_v, const AttnParams p) {
@@ -292,9 +292,19 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
     const int m_block = blockIdx.x % p.m_blocks;
     const int bh = blockIdx.x / p.m_blocks;
     const int head = bh % p.H, batch = bh / p.H;
-    const int n_iters = p.n_tiles;
-    const int j0 = p.mid_window < 0 ? p.n_tiles - 1
-                                    : min(2 * m_block + p.first_tile + p.mid_window, p.n_tiles - 1);
+    // Causal (bottom-right aligned, cute/mask.py:186-199): key column c is visible to query row r iff
+    // c < r + 1 + Sk - Sq, so this CTA's rows need the tiles below `visible` only (at least one tile is
+    // visited: fully masked rows then end with a zero denominator and produce zeros).
+    int visible = p.n_tiles;
+    if (kCausal) {
+        const long long last_row = min(static_cast<long long>(m_block + 1) * (2 * kTile), p.Sq) - 1;
+        const long long limit = last_row + 1 + p.Sk - p.Sq;  // columns < limit
+        visible = static_cast<int>(max(1LL, min(static_cast<long long>(p.n_tiles), (limit + kTile - 1) / kTile)));
+    }
+    const int n_tiles = visible;  // tiles this CTA visits (all of them unless causal)
+    const int n_iters = n_tiles;
+    const int j0 = p.mid_window < 0 ? n_tiles - 1
+                                    : min(2 * m_block + p.first_tile + p.mid_window, n_tiles - 1);
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < 2; ++i) {
@@ -351,7 +361,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
                 }
                 int issued_k = 0, issued_v = 0;
                 for (int it = 0; it < n_iters; ++it) {
-                    const int j = tile_at(it, j0, p.first_tile, p.n_tiles);
+                    const int j = tile_at(it, j0, p.first_tile, n_tiles);
                     const int ks = it % kKStages, vs = it % kVStages;
                     // K(it - kKStages) was last read by stage 1's QK of that step; stage 1 releases the slot
                     // when it sees those scores.
@@ -477,7 +487,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         int j_prev = 0;        // V-Smooth: key tile of the previous step
         bool ok = true;
         for (int it = 0; it < n_iters; ++it) {
-            const int j = tile_at(it, j0, p.first_tile, p.n_tiles);
+            const int j = tile_at(it, j0, p.first_tile, n_tiles);
             const float kd = __ldg(kd_row + j);
             if ((warp & 3) == 0) OVC_TL(it, stage * 6 + 0);
             ok = __all_sync(0xFFFFFFFFu, wait_bar(sm, &sm.s_full[stage], it & 1, p.status));
@@ -505,6 +515,17 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
 #pragma unroll
                 for (int c = 0; c < 128; ++c)
                     if (c >= tail_valid) s[c] = 0xFF800000u;  // -inf
+            }
+            if (kCausal) {
+                // Columns of this tile that row `row` may see: c < row + 1 + Sk - Sq - 128 j.
+                const long long first_row = static_cast<long long>(q_tile) * kTile;
+                if (static_cast<long long>(j) * kTile + kTile - 1 > first_row + p.Sk - p.Sq) {  // some row of the tile is cut
+                    const long long limit = first_row + row_in_tile + 1 + p.Sk - p.Sq - static_cast<long long>(j) * kTile;
+                    const int visible_columns = static_cast<int>(max(0LL, min(static_cast<long long>(kTile), limit)));
+#pragma unroll
+                    for (int c = 0; c < 128; ++c)
+                        if (c >= visible_columns) s[c] = 0xFF800000u;  // -inf
+                }
             }
             if (j < p.first_tile) {
                 // Repair keys come from different K blocks: each column carries its own K descale.
@@ -718,8 +739,10 @@ namespace {
 
 int launch_attention(const void* q8, const void* k8, const void* v_packed, const float* q_descale, int64_t q_blocks,
                      const float* k_descale, const float* v_descale, const float* repair_kd, int64_t repair_rows,
-                     const float* vs_means, const float* vs_scale, void* out, float* lse, int64_t B, int64_t Sq,
-                     int64_t Sk, int64_t H, float softmax_scale, int mid_window_blocks, uint32_t* status, void* stream) {
+                     const float* vs_means, const float* vs_scale, void* out, float* lse, int causal, int64_t B,
+                     int64_t Sq, int64_t Sk, int64_t H, float softmax_scale, int mid_window_blocks, uint32_t* status,
+                     void* stream) {
+    if (causal && (mid_window_blocks != -1 || repair_rows != 0 || vs_means != nullptr)) return OVC_ERR_ARGUMENT;
     if (!q8 || !k8 || !v_packed || !q_descale || !k_descale || !v_descale || !out || B < 1 || Sq < 1 || Sk < 1 ||
         H < 1 || Sq > (1LL << 30) || Sk > (1LL << 30) || q_blocks < ceil_div(Sq, kTile) || !(softmax_scale > 0.0f) ||
         !isfinite(softmax_scale) || mid_window_blocks < -1 || repair_rows < 0 || repair_rows % kTile != 0 ||
@@ -768,16 +791,19 @@ int launch_attention(const void* q8, const void* k8, const void* v_packed, const
     const size_t smem_bytes = sizeof(SmemLayout) + 1024;
     static bool configured[64] = {};
     if (device < 64 && !configured[device]) {
-        err = cudaFuncSetAttribute(attention_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem_bytes));
+        err = cudaFuncSetAttribute(attention_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem_bytes));
         if (err == cudaSuccess)
-            err = cudaFuncSetAttribute(attention_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem_bytes));
+            err = cudaFuncSetAttribute(attention_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem_bytes));
+        if (err == cudaSuccess)
+            err = cudaFuncSetAttribute(attention_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem_bytes));
         if (err != cudaSuccess) { set_last_cuda_error(err); return OVC_ERR_CUDA; }
         configured[device] = true;
     }
     const unsigned grid = static_cast<unsigned>(m_blocks * H * B);
     auto s = static_cast<cudaStream_t>(stream);
-    if (vs_means != nullptr) attention_kernel<true><<<grid, kThreads, smem_bytes, s>>>(map_q, map_k, map_v, p);
-    else attention_kernel<false><<<grid, kThreads, smem_bytes, s>>>(map_q, map_k, map_v, p);
+    if (vs_means != nullptr) attention_kernel<true, false><<<grid, kThreads, smem_bytes, s>>>(map_q, map_k, map_v, p);
+    else if (causal) attention_kernel<false, true><<<grid, kThreads, smem_bytes, s>>>(map_q, map_k, map_v, p);
+    else attention_kernel<false, false><<<grid, kThreads, smem_bytes, s>>>(map_q, map_k, map_v, p);
     return check_launch();
 }
 
@@ -788,16 +814,15 @@ extern "C" int ovc_attention(const void* q8, const void* k8, const void* v_packe
                              int64_t repair_rows, void* out, int64_t B, int64_t Sq, int64_t Sk, int64_t H,
                              float softmax_scale, int mid_window_blocks, uint32_t* status, void* stream) {
     return launch_attention(q8, k8, v_packed, q_descale, q_blocks, k_descale, v_descale, repair_kd, repair_rows, nullptr,
-                            nullptr, out, nullptr, B, Sq, Sk, H, softmax_scale, mid_window_blocks, status, stream);
+                            nullptr, out, nullptr, 0, B, Sq, Sk, H, softmax_scale, mid_window_blocks, status, stream);
 }
 
-extern "C" int ovc_attention_lse(const void* q8, const void* k8, const void* v_packed, const float* q_descale,
-                                 int64_t q_blocks, const float* k_descale, const float* v_descale, const float* repair_kd,
-                                 int64_t repair_rows, void* out, float* lse, int64_t B, int64_t Sq, int64_t Sk, int64_t H,
-                                 float softmax_scale, int mid_window_blocks, uint32_t* status, void* stream) {
-    if (lse == nullptr) return OVC_ERR_ARGUMENT;
+extern "C" int ovc_attention_ex(const void* q8, const void* k8, const void* v_packed, const float* q_descale,
+                                int64_t q_blocks, const float* k_descale, const float* v_descale, const float* repair_kd,
+                                int64_t repair_rows, void* out, float* lse, int causal, int64_t B, int64_t Sq, int64_t Sk,
+                                int64_t H, float softmax_scale, int mid_window_blocks, uint32_t* status, void* stream) {
     return launch_attention(q8, k8, v_packed, q_descale, q_blocks, k_descale, v_descale, repair_kd, repair_rows, nullptr,
-                            nullptr, out, lse, B, Sq, Sk, H, softmax_scale, mid_window_blocks, status, stream);
+                            nullptr, out, lse, causal, B, Sq, Sk, H, softmax_scale, mid_window_blocks, status, stream);
 }
 
 extern "C" int ovc_attention_vsmooth(const void* q8, const void* k8, const void* v_packed, const float* unit_descale,
@@ -808,5 +833,5 @@ extern "C" int ovc_attention_vsmooth(const void* q8, const void* k8, const void*
     const int64_t blocks = ceil_div(Sq > Sk ? Sq : Sk, kTile);
     // unit_descale: at least H * ceil(max(Sq,Sk)/128) floats equal to 1.0 (no Q/K/V descales on this path).
     return launch_attention(q8, k8, v_packed, unit_descale, blocks, unit_descale, unit_descale, nullptr, 0, means,
-                            channel_scale, out, nullptr, 1, Sq, Sk, H, softmax_scale, mid_window_blocks, status, stream);
+                            channel_scale, out, nullptr, 0, 1, Sq, Sk, H, softmax_scale, mid_window_blocks, status, stream);
 }

@@ -3,8 +3,8 @@
 Takes the argument contract that the reference's public functions hand to its kernel interface
 ``_flash_attn_fwd(q, k, v, **kwargs) -> (out, lse)``
 (src/open_vc_attn/_kernels/blackwell/flash_attn/cute/interface.py:110-179), restricted to what
-those functions use: FP8 E4M3 Q/K/V with FP32 descales, ExpCast, non-causal, no LSE, optional
-prepacked V and optional repair prefix.  Anything else raises instead of degrading.
+those functions use: FP8 E4M3 Q/K/V with FP32 descales, ExpCast, optional causal mask, optional LSE,
+optional prepacked V and optional repair prefix.  Anything else raises instead of degrading.
 """
 
 import math
@@ -90,8 +90,8 @@ def flash_attn_fwd(
         raise NotImplementedError(f"Unsupported kernel options in this build: {sorted(unsupported)}")
     if not expcast:
         raise NotImplementedError("Only the ExpCast FP8 path (expcast=True) is built")
-    if causal:
-        raise NotImplementedError("causal=True is not built; this engine is dense non-causal attention")
+    if causal and (mid_window_blocks is not None or repair_k_descale is not None or v_smooth):
+        raise ValueError("causal attention uses the plain key scan (mid_window_blocks=None) and takes no repair prefix or V-Smooth")
     if any(t.dtype != torch.float8_e4m3fn for t in (q, k, v)):
         raise ValueError("ExpCast attention expects float8_e4m3fn Q/K/V")
     if v_smooth:
@@ -171,14 +171,16 @@ def flash_attn_fwd(
         repair_ptr = None if repair_k_descale is None else repair_k_descale.data_ptr()
         tail = (batch, sq, sk, heads, float(softmax_scale), window, status_word(device).data_ptr(), _lib.stream_pointer(device))
         lse = None
-        if return_lse:
-            lse = torch.empty((batch, heads, sq) if q.ndim == 4 else (heads, sq), dtype=torch.float32, device=device)
+        if return_lse or causal:
+            if return_lse:
+                lse = torch.empty((batch, heads, sq) if q.ndim == 4 else (heads, sq), dtype=torch.float32, device=device)
             _lib.check(
-                lib.ovc_attention_lse(
+                lib.ovc_attention_ex(
                     q.data_ptr(), k.data_ptr(), packed_ptr, q_descale.data_ptr(), q_descale.shape[2], k_descale.data_ptr(),
-                    v_descale.data_ptr(), repair_ptr, repair_rows, out.data_ptr(), lse.data_ptr(), *tail,
+                    v_descale.data_ptr(), repair_ptr, repair_rows, out.data_ptr(), None if lse is None else lse.data_ptr(),
+                    1 if causal else 0, *tail,
                 ),
-                "ovc_attention_lse",
+                "ovc_attention_ex",
             )
         else:
             _lib.check(

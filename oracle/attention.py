@@ -110,6 +110,7 @@ def expcast_attention(
     v_smooth_means=None,
     v_channel_scale=None,
     return_lse=False,
+    causal=False,
 ):
     """ExpCast attention for one (batch item, head set) on FP8 codes.
 
@@ -122,6 +123,8 @@ def expcast_attention(
     probabilities) x (its block mean) to the accumulator and the result is scaled per channel.
     Returns float32 [Sq,H,128] already rounded to bfloat16 precision; with ``return_lse`` also the float32
     log-sum-exp [H,Sq] = (m*sigma + log2(l) - 8) ln 2, -inf where l is 0 or NaN (fwd:4437-4475).
+    ``causal``: key column c is visible to query row r iff c < r + 1 + Sk - Sq (cute/mask.py:186-199); a 256-row
+    block visits only the tiles that one of its rows can see (at least one), in the plain descending order.
     """
     sq, h, d = q8.shape
     sk = k8.shape[0]
@@ -146,7 +149,13 @@ def expcast_attention(
 
     for head in range(h):
         for m_block in todo:
-            order = tile_order(n_tiles, first_tile, m_block, mid_window_blocks)
+            if causal:
+                assert mid_window_blocks is None and first_tile == 0
+                limit = min((m_block + 1) * 2 * TILE, sq) + sk - sq  # columns below this are visible to the block's last row
+                visible = max(1, min(n_tiles, (limit + TILE - 1) // TILE))
+                order = list(range(visible - 1, -1, -1))
+            else:
+                order = tile_order(n_tiles, first_tile, m_block, mid_window_blocks)
             for stage in range(2):
                 q_tile = 2 * m_block + stage
                 r0 = q_tile * TILE
@@ -165,6 +174,10 @@ def expcast_attention(
                     s_raw = (q_rows @ kf[c0 : c0 + TILE, head].T).astype(F32)
                     if tile == n_tiles - 1 and sk - c0 < TILE:
                         s_raw[:, sk - c0 :] = -np.inf
+                    if causal:
+                        columns = c0 + np.arange(TILE)[None, :]
+                        rows_here = np.arange(r0, r1)[:, None]
+                        s_raw = np.where(columns < rows_here + 1 + sk - sq, s_raw, F32(-np.inf)).astype(F32)
                     if tile < first_tile:
                         s_raw = (s_raw * repair_k_descale[head, c0 : c0 + TILE][None, :]).astype(F32)
                         kd = F32(1.0)
@@ -214,7 +227,7 @@ def _round_bf16(x):
     return rounded.astype(np.uint32).view(F32)
 
 
-def exact_attention(q, k, v, softmax_scale=None, rows=None):
+def exact_attention(q, k, v, softmax_scale=None, rows=None, causal=False):
     """Exact softmax attention in float64 (tests/gpu/test_attention.py:18-24 in the reference).
 
     q [Sq,H,128], k/v [Sk,H,128] float arrays.  ``rows``: optional index array of query rows.
@@ -223,15 +236,20 @@ def exact_attention(q, k, v, softmax_scale=None, rows=None):
     q = np.asarray(q, dtype=F64)
     k = np.asarray(k, dtype=F64)
     v = np.asarray(v, dtype=F64)
+    full_rows = q.shape[0]
     if rows is not None:
         q = q[rows]
     tau = 1.0 / math.sqrt(q.shape[-1]) if softmax_scale is None else float(softmax_scale)
     out = np.empty(q.shape, dtype=F64)
     for head in range(q.shape[1]):
         s = (q[:, head] @ k[:, head].T) * tau
-        s -= s.max(axis=1, keepdims=True)
-        p = np.exp(s)
-        out[:, head] = (p @ v[:, head]) / p.sum(axis=1, keepdims=True)
+        if causal:
+            row_index = (np.arange(q.shape[0]) if rows is None else np.asarray(rows))[:, None]
+            s = np.where(np.arange(k.shape[0])[None, :] < row_index + 1 + k.shape[0] - full_rows, s, -np.inf)
+        top = s.max(axis=1, keepdims=True)
+        p = np.exp(s - np.where(np.isneginf(top), 0.0, top))
+        total = p.sum(axis=1, keepdims=True)
+        out[:, head] = (p @ v[:, head]) / np.where(total == 0, 1.0, total)
     return out
 
 

@@ -120,8 +120,6 @@ def test_validation_errors():
         ovc.attention(q, q, q.float())
     with pytest.raises(ValueError, match="detach"):
         ovc.attention(q.clone().requires_grad_(), q, q)
-    with pytest.raises(NotImplementedError, match="causal"):
-        ovc.attention(q, q, q, causal=True)
     with pytest.raises(ValueError, match="not available"):
         ovc.attention(q, q, q, mode="bf16", version="reference")
     prepared = api.prepare_fp8(q, q, q)
@@ -244,3 +242,29 @@ def test_log_sum_exp_output(shape):
         long_q = torch.randn(32768, 1, 128, device=DEV, dtype=torch.bfloat16)
         with pytest.raises(ValueError, match="without LSE"):  # src/open_vc_attn/api.py:152-153 of the reference
             api.attention_fp8(api.prepare_fp8_fused(long_q, long_q, long_q), return_lse=True)
+
+
+@pytest.mark.parametrize("sq,sk,h", [(300, 300, 2), (1024, 1024, 1), (200, 520, 2), (520, 200, 1)])
+def test_causal_mask(sq, sk, h):
+    """causal=True (bottom-right aligned for Sq != Sk): against the oracle and exact masked attention."""
+    ovc, api, forward = _api()
+    torch.manual_seed(sq + sk)
+    q = torch.randn(sq, h, 128, device=DEV, dtype=torch.bfloat16)
+    k, v = [torch.randn(sk, h, 128, device=DEV, dtype=torch.bfloat16) for _ in range(2)]
+    out, lse = ovc.attention(q, k, v, causal=True, return_lse=True)
+    forward.check_status(q.device)
+    assert torch.isfinite(out).all()
+    pq, pk, pv = oprep.quantize_per_block(f32(q)[None]), oprep.quantize_per_block(f32(k)[None]), oprep.quantize_per_head(f32(v)[None])
+    want, want_lse = oatt.expcast_attention(pq[0][0], pk[0][0], pv[0][0], pq[1][0], pk[1][0], pv[1][0], mid_window_blocks=None,
+                                            causal=True, return_lse=True)
+    assert oatt.relative_l2(f32(out), want) < ORACLE_TOL
+    seen = np.isfinite(want_lse)
+    assert np.array_equal(np.isfinite(f32(lse)), seen) and np.abs(f32(lse)[seen] - want_lse[seen]).max() < 2e-3
+    assert oatt.relative_l2(f32(out), oatt.exact_attention(f32(q), f32(k), f32(v), causal=True)) < 0.10
+    if sq > sk:  # rows that see no key at all give zeros and -inf
+        hidden = sq - sk
+        assert not f32(out)[:hidden].any() and np.isneginf(f32(lse)[:, :hidden]).all()
+    prepared = api.prepare_fp8(q, k, v)
+    with pytest.raises(ValueError, match="plain key scan"):
+        api.raw_forward(prepared.q, prepared.k, prepared.v, q_descale=prepared.q_descale, k_descale=prepared.k_descale,
+                        v_descale=prepared.v_descale, expcast=True, causal=True, mid_window_blocks=4)

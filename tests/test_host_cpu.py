@@ -80,8 +80,8 @@ def test_unbuilt_options_raise_instead_of_degrading():
     d3 = torch.ones(1, 2, 1)
     d2 = torch.ones(1, 2)
     common = dict(q_descale=d3, k_descale=d3, v_descale=d2, expcast=True)
-    with pytest.raises(NotImplementedError, match="causal"):
-        forward.flash_attn_fwd(q, q, q, causal=True, **common)
+    with pytest.raises(ValueError, match="plain key scan"):
+        forward.flash_attn_fwd(q, q, q, causal=True, mid_window_blocks=4, **common)
     with pytest.raises(NotImplementedError, match="Unsupported kernel options"):
         forward.flash_attn_fwd(q, q, q, v_smooth_head_major=True, **common)
     with pytest.raises(NotImplementedError, match="takes no descales"):
