@@ -9,8 +9,8 @@ Follows src/open_vc_attn/_kernels/blackwell/v_smooth.py of the reference:
 Parity status: unpinned.  The reference's grouping uses BF16 tensor-core products whose accumulation
 order is not specified, so labels of near-tied tokens (and with them the permutation) can differ between
 implementations; tests therefore replay a given permutation and compare everything downstream of it.
-Block sums are taken over the 128 rows in ascending order in float32, one channel at a time, which is the
-order the CUDA kernel uses; the reference's Triton reduction order is unspecified.
+Block sums are taken in float32 in the fixed two-level order of the CUDA kernel (see block_sum); the
+reference's Triton reduction order is unspecified.
 """
 
 import numpy as np
@@ -58,6 +58,21 @@ def kmeans_permutation(v, clusters=64, iterations=4):
     return permutation, centers, labels
 
 
+def block_sum(rows):
+    """Float32 sum over the rows of one block in the fixed order of the CUDA kernel: rows g + 16 i are added in
+    ascending i into sixteen partial sums, which are then added in ascending g (missing rows count as 0)."""
+    padded = np.zeros((BLOCK, rows.shape[1]), dtype=F32)
+    padded[: rows.shape[0]] = rows
+    lanes = padded.reshape(8, 16, -1)
+    partial = lanes[0].copy()
+    for i in range(1, 8):
+        partial = (partial + lanes[i]).astype(F32)
+    total = partial[0].copy()
+    for g in range(1, 16):
+        total = (total + partial[g]).astype(F32)
+    return total
+
+
 def apply_v_smooth(q, k, v, permutation):
     """Permute K/V by group, demean V per 128-token block, quantise.  q,k,v float32 [S,H,128] (BF16 values),
     permutation int [H,S].  Returns dict(q, k, v codes uint8 [S,H,128], means f32 [blocks,H,128] (BF16-rounded,
@@ -75,10 +90,7 @@ def apply_v_smooth(q, k, v, permutation):
         amax = np.zeros(d, dtype=F32)
         for b in range(blocks):
             rows = vp[b * BLOCK : (b + 1) * BLOCK]
-            total = np.zeros(d, dtype=F32)
-            for r in range(rows.shape[0]):  # ascending row order, float32
-                total = (total + rows[r]).astype(F32)
-            means[b] = (total / F32(rows.shape[0])).astype(F32)
+            means[b] = (block_sum(rows) / F32(rows.shape[0])).astype(F32)
             amax = np.maximum(amax, np.abs((rows - means[b][None, :]).astype(F32)).max(axis=0))
         scale = np.where(amax > 0, (amax / F32(448.0)).astype(F32), F32(1.0)).astype(F32)
         for b in range(blocks):
