@@ -190,8 +190,8 @@ int ovc_attention_ex(const void* q8, const void* k8, const void* v_packed, const
 /*
  * labels[h][s] = argmin_k (|c_k|^2 - 2 v_s.c_k), first index on ties (_assign_values, v_smooth.py:10-39).
  *   v [S,H,128] bf16, centers [H,K,128] bf16, labels [H,S] int32 out; 1 <= K <= min(128, S).
- * Products are accumulated in float32 by fused multiply-adds over ascending channels; the reference's
- * BF16 tensor-core product has an unspecified order, so near-tied tokens may be labelled differently.
+ * The products are BF16 x BF16 -> FP32 tensor-core MMAs, as in the reference; the accumulation order of
+ * such a product is not specified on either side, so near-tied tokens may be labelled differently.
  */
 int ovc_vs_assign(const void* v, const void* centers, int32_t* labels, int64_t S, int64_t H, int64_t K, void* stream);
 
@@ -208,7 +208,8 @@ int ovc_vs_update_centers(const float* sums, const float* counts, void* centers,
 /*
  * Block means of V in group order and the per-channel maximum of |v - mean| (_block_stats, v_smooth.py:76-94).
  *   permutation [H,S] int64; means [H,ceil(S/128),128] f32 out; amax [H,128] f32 out (cleared first).
- * A block's rows are summed in ascending order in float32.
+ * A channel's sum over a block is taken in float32 in a fixed order: rows g + 16 i in ascending i into
+ * sixteen partial sums, then the partial sums in ascending g; rows past the end of the sequence count as 0.
  */
 int ovc_vs_block_stats(const void* v, const int64_t* permutation, float* means, float* amax, int64_t S, int64_t H,
                        void* stream);
