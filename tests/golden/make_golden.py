@@ -23,7 +23,9 @@ import os
 import sys
 
 os.environ["TRITON_INTERPRET"] = "1"
-sys.path.insert(0, os.environ.get("REFERENCE_SRC", "/root/reference/src"))
+if "REFERENCE_SRC" not in os.environ:
+    raise SystemExit("set REFERENCE_SRC to the src/ directory of an open-vc-attention 0.3.0 checkout")
+sys.path.insert(0, os.environ["REFERENCE_SRC"])
 
 import numpy as np  # noqa: E402
 import torch  # noqa: E402
