@@ -14,8 +14,6 @@
 namespace ovc {
 namespace {
 
-__device__ __forceinline__ float bf16_bits_to_float(uint16_t b) { return __uint_as_float(static_cast<uint32_t>(b) << 16); }
-
 __device__ __forceinline__ uint8_t to_e4m3(float x) {
     return static_cast<uint8_t>(__nv_cvt_float_to_fp8(x, __NV_SATFINITE, __NV_E4M3));
 }
