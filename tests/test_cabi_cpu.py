@@ -68,3 +68,18 @@ def test_null_and_bad_arguments_are_rejected_without_a_gpu(lib):
     assert lib.ovc_attention(p, p, p, p, 1, p, p, p, 100, p, 1, 128, 256, 1, 0.1, 4, null, null) == bad     # R % 128
     assert lib.ovc_attention(p, p, p, p, 0, p, p, null, 0, p, 1, 128, 128, 1, 0.1, 4, null, null) == bad    # q_blocks
     assert lib.ovc_attention(p, p, p, p, 1, p, p, null, 0, p, 1, 128, 128, 1, 0.1, -2, null, null) == bad   # window
+    # extended attention entry, V-Smooth attention and preparation entries
+    assert lib.ovc_attention_ex(null, null, null, null, 1, null, null, null, 0, null, null, 0, 1, 128, 128, 1, 0.1, -1, null, null) == bad
+    assert lib.ovc_attention_ex(p, p, p, p, 1, p, p, null, 0, p, null, 1, 1, 128, 128, 1, 0.1, 4, null, null) == bad   # causal + window
+    assert lib.ovc_attention_ex(p, p, p, p, 1, p, p, p, 128, p, null, 1, 1, 128, 256, 1, 0.1, -1, null, null) == bad   # causal + repair
+    assert lib.ovc_attention_vsmooth(p, p, p, p, null, p, p, 128, 128, 1, 0.1, -1, null, null) == bad                   # no means
+    assert lib.ovc_attention_vsmooth(p, p, p, p, p + 4, p, p, 128, 128, 1, 0.1, -1, null, null) == bad                  # misaligned means
+    assert lib.ovc_vs_assign(null, null, null, 128, 1, 8, null) == bad
+    assert lib.ovc_vs_assign(p, p, p, 128, 1, 129, null) == bad            # more than 128 clusters
+    assert lib.ovc_vs_assign(p, p, p, 4, 1, 8, null) == bad                # more clusters than tokens
+    assert lib.ovc_vs_accumulate(p, p, null, p, 128, 1, 8, null) == bad
+    assert lib.ovc_vs_update_centers(null, p, p, 1, 8, null) == bad
+    assert lib.ovc_vs_block_stats(p, null, p, p, 128, 1, null) == bad
+    assert lib.ovc_vs_block_write(p, p, p, p, p, p, null, p, p, 128, 1, null) == bad
+    assert lib.ovc_cast_e4m3(p, 1, p, 12, null) == bad                     # not a multiple of 8
+    assert lib.ovc_cast_e4m3(p, 9, p, 16, null) == bad                     # dtype
