@@ -166,6 +166,17 @@ int ovc_attention(const void* q8, const void* k8, const void* v_packed, const fl
                   float softmax_scale, int mid_window_blocks, uint32_t* status, void* stream);
 
 /*
+ * Copies `heads` consecutive heads of a [S, src_heads, bytes_per_head] tensor into a
+ * [S, dst_heads, bytes_per_head] tensor (one strided 2-D copy on `stream`), host to device when
+ * to_device is non-zero, else device to host; the host side should be pinned memory for the copy to be
+ * asynchronous.  Has no counterpart in the reference, whose callers keep Q, K, V on the device: it lets a
+ * caller with host-resident tensors stream head groups through the GPU (heads are independent on this path),
+ * overlapping the copies with the kernels of the previous group.
+ */
+int ovc_copy_head_slice(void* dst, int64_t dst_heads, int64_t dst_first, const void* src, int64_t src_heads,
+                        int64_t src_first, int64_t heads, int64_t S, int64_t bytes_per_head, int to_device, void* stream);
+
+/*
  * ovc_attention with the two options of _flash_attn_fwd that the default call does not use
  * (cute/interface.py:122,139-143):
  *   lse     [B,H,Sq] f32 or NULL: log-sum-exp of the scaled scores of every query row,

@@ -541,6 +541,24 @@ int ovc_pack_v(const void* codes, int64_t B, int64_t S, int64_t H, void* packed,
     return check_launch();
 }
 
+int ovc_copy_head_slice(void* dst, int64_t dst_heads, int64_t dst_first, const void* src, int64_t src_heads,
+                        int64_t src_first, int64_t heads, int64_t S, int64_t bytes_per_head, int to_device, void* stream) {
+    if (!dst || !src || S < 1 || heads < 1 || bytes_per_head < 1 || dst_first < 0 || src_first < 0 ||
+        dst_first + heads > dst_heads || src_first + heads > src_heads)
+        return OVC_ERR_ARGUMENT;
+    // One 2-D copy: S rows (tokens) of `heads` consecutive heads each; the row pitch is the tensor's head count.
+    const cudaError_t err = cudaMemcpy2DAsync(
+        static_cast<char*>(dst) + dst_first * bytes_per_head, static_cast<size_t>(dst_heads * bytes_per_head),
+        static_cast<const char*>(src) + src_first * bytes_per_head, static_cast<size_t>(src_heads * bytes_per_head),
+        static_cast<size_t>(heads * bytes_per_head), static_cast<size_t>(S),
+        to_device ? cudaMemcpyHostToDevice : cudaMemcpyDeviceToHost, static_cast<cudaStream_t>(stream));
+    if (err != cudaSuccess) {
+        set_last_cuda_error(static_cast<int>(err));
+        return OVC_ERR_CUDA;
+    }
+    return OVC_OK;
+}
+
 int ovc_repair_score(const void* v, int dtype, int64_t S, int64_t H, const float* amax, void* codes, float* score,
                      void* stream) {
     if (!v || !amax || !codes || !score || bad_dims(1, S, H) || (dtype != OVC_F16 && dtype != OVC_BF16) ||

@@ -268,3 +268,26 @@ def test_causal_mask(sq, sk, h):
     with pytest.raises(ValueError, match="plain key scan"):
         api.raw_forward(prepared.q, prepared.k, prepared.v, q_descale=prepared.q_descale, k_descale=prepared.k_descale,
                         v_descale=prepared.v_descale, expcast=True, causal=True, mid_window_blocks=4)
+
+
+@pytest.mark.parametrize("s,h,group", [(700, 5, 2), (1024, 8, 8), (2000, 3, 4)])
+def test_host_streaming_equals_the_device_call(s, h, group):
+    """attention_host: head groups streamed from pinned host memory give the device result bit for bit."""
+    ovc, api, forward = _api()
+    from open_vc_attn import streaming
+
+    torch.manual_seed(s)
+    host = [torch.randn(s, h, 128, dtype=torch.bfloat16).pin_memory() for _ in range(3)]
+    want = ovc.attention(*[t.to(DEV) for t in host])
+    out = streaming.attention_host(*host, device=DEV, heads_per_group=group)
+    torch.cuda.synchronize()
+    forward.check_status(torch.device(DEV))
+    assert out.is_pinned() and torch.equal(out, want.cpu())
+    runner = streaming.HostAttention(s, h, torch.bfloat16, DEV, heads_per_group=group)
+    again = torch.empty_like(out).pin_memory()
+    for _ in range(3):  # buffers and events are reused across calls
+        runner(*host, out=again)
+    torch.cuda.synchronize()
+    assert torch.equal(again, want.cpu())
+    with pytest.raises(ValueError, match="pinned"):
+        streaming.attention_host(*[t.clone() for t in host], device=DEV)
