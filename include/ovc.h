@@ -121,6 +121,14 @@ int ovc_prepare_fused_static(const void* q, const void* k, const void* v, int dt
 int ovc_pack_v(const void* codes, int64_t B, int64_t S, int64_t H, void* packed, void* stream);
 
 /*
+ * q[i] = a[i] / b[i] with the division instruction the preparation kernels use (div.full.f32: the
+ * dividend times the hardware's approximate reciprocal, which is what Triton emits for the `/` in
+ * src/open_vc_attn/quantization.py:183-184, preparation.py:43-46,79 and v_repair.py:69-70,111).
+ * For callers and tests that need the exact scales on the host; a, b, q: n floats in device memory.
+ */
+int ovc_div_full(const float* a, const float* b, float* q, int64_t n, void* stream);
+
+/*
  * V cast plus per-token squared rounding residual.  Replaces _v_quant_score_kernel
  * (src/open_vc_attn/v_repair.py:52-76).
  *   v [S,H,128] f16/bf16, amax [H] f32 -> codes [S,H,128] fp8, score [H,S] f32.

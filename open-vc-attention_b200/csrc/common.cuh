@@ -27,4 +27,14 @@ constexpr int kDim = 128;   // head dimension
 
 inline int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
 
+#ifdef __CUDACC__
+// a / b as the reference's Triton kernels compute it on a GPU: div.full.f32, the dividend times the
+// hardware's approximate reciprocal of b, rounded once (not the IEEE quotient).
+__device__ __forceinline__ float div_full(float a, float b) {
+    float q;
+    asm("div.full.f32 %0, %1, %2;" : "=f"(q) : "f"(a), "f"(b));
+    return q;
+}
+#endif
+
 }  // namespace ovc

@@ -3,8 +3,12 @@
 // Arithmetic follows the reference's Triton kernels operation for operation
 // (src/open_vc_attn/quantization.py, src/open_vc_attn/preparation.py,
 // src/open_vc_attn/v_repair.py in the reference project): amax floored at 1e-12,
-// one IEEE division 448/amax, one multiply, clamp to +-448, round-to-nearest-even
-// E4M3 cast.  Every global access is a 16-byte (or 8-byte for FP8 rows) vector
+// one division 448/amax, one multiply, clamp to +-448, round-to-nearest-even E4M3
+// cast.  Triton lowers a float32 `/` to div.full.f32 (the dividend times an
+// approximate reciprocal, not the IEEE quotient) and contracts `x - c * d` into one
+// FMA; the kernels here issue the same instructions, because inputs with few mantissa
+// bits put many scaled values exactly on E4M3 rounding ties, where the last bit of the
+// scale decides the code.  Every global access is a 16-byte (or 8-byte for FP8 rows) vector
 // access covering whole 128-byte lines per warp.
 
 #include <cuda_bf16.h>
@@ -156,9 +160,9 @@ __global__ void __launch_bounds__(256, 2) quant_block_kernel(BlockQuantArgs a, l
             m = absmax8(f, m);
         }
         const float amax = fmaxf(cta256_max(m, part[blk & 1]), kFloor);
-        const float scale = __fdiv_rn(kQMax, amax);
+        const float scale = div_full(kQMax, amax);
         if (threadIdx.x == 0) {
-            descale[blk] = __fdiv_rn(amax, kQMax);
+            descale[blk] = div_full(amax, kQMax);
             if (blk == 0 && a.descale_stride[which] > blocks) descale[blocks] = 1.0f;
             if (blk == 0 && which == 0 && a.amax_init != nullptr) a.amax_init[batch * H + head] = 0.0f;
         }
@@ -215,8 +219,8 @@ __global__ void __launch_bounds__(128) head_cast_kernel(const void* v, const flo
     const uint16_t* src = static_cast<const uint16_t*>(v) + batch * S * row_pitch + head * kDim + c16 * 8;
     uint8_t* dst = codes + batch * S * row_pitch + head * kDim + c16 * 8;
     const float amax = fmaxf(amax_in[batch * H + head], kFloor);
-    const float scale = __fdiv_rn(kQMax, amax);
-    const float descale = __fdiv_rn(amax, kQMax);
+    const float scale = div_full(kQMax, amax);
+    const float descale = div_full(amax, kQMax);
     if (descale_out != nullptr && blk == 0 && threadIdx.x == 0) descale_out[batch * H + head] = descale;
     uint4 raw[16];
 #pragma unroll
@@ -237,7 +241,7 @@ __global__ void __launch_bounds__(128) head_cast_kernel(const void* v, const flo
             float sum = 0.0f;
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
-                const float r = __fsub_rn(f[j], __fmul_rn(dec[j], descale));
+                const float r = __fmaf_rn(-dec[j], descale, f[j]);
                 sum = __fadd_rn(sum, __fmul_rn(r, r));
             }
 #pragma unroll
@@ -293,9 +297,9 @@ __global__ void __launch_bounds__(256) cast_pack_kernel(const void* v, const flo
     const long long row_pitch = static_cast<long long>(H) * kDim;
     const uint16_t* src = static_cast<const uint16_t*>(v) + batch * S * row_pitch + head * kDim + l16 * 8;
     const float amax = fmaxf(amax_in[batch * H + head], kFloor);
-    const float scale = __fdiv_rn(kQMax, amax);
+    const float scale = div_full(kQMax, amax);
     if (descale_out != nullptr && tile == 0 && threadIdx.x == 0)
-        descale_out[batch * H + head] = __fdiv_rn(amax, kQMax);
+        descale_out[batch * H + head] = div_full(amax, kQMax);
     uint4 raw[8];
 #pragma unroll
     for (int gi = 0; gi < 2; ++gi)
@@ -389,10 +393,15 @@ __global__ void __launch_bounds__(32) repair_rows_kernel(uint8_t* k_all, uint8_t
     float c[4];
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
-        const float residual = real ? __fsub_rn(o[j], __fmul_rn(d[j], descale)) : 0.0f;
-        c[j] = clamp448(__fdiv_rn(residual, descale));
+        const float residual = real ? __fmaf_rn(-d[j], descale, o[j]) : 0.0f;
+        c[j] = clamp448(div_full(residual, descale));
     }
     *reinterpret_cast<uint32_t*>(v_all + target) = cast4(c[0], c[1], c[2], c[3]);
+}
+
+__global__ void div_full_kernel(const float* a, const float* b, float* q, long long n) {
+    const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i < n) q[i] = div_full(a[i], b[i]);
 }
 
 bool bad_dims(int64_t B, int64_t S, int64_t H) {
@@ -557,6 +566,12 @@ int ovc_copy_head_slice(void* dst, int64_t dst_heads, int64_t dst_first, const v
         return OVC_ERR_CUDA;
     }
     return OVC_OK;
+}
+
+int ovc_div_full(const float* a, const float* b, float* q, int64_t n, void* stream) {
+    if (!a || !b || !q || n < 1 || ceil_div(n, 256) > 0x7FFFFFFF) return OVC_ERR_ARGUMENT;
+    div_full_kernel<<<static_cast<unsigned>(ceil_div(n, 256)), 256, 0, static_cast<cudaStream_t>(stream)>>>(a, b, q, n);
+    return check_launch();
 }
 
 int ovc_repair_score(const void* v, int dtype, int64_t S, int64_t H, const float* amax, void* codes, float* score,

@@ -232,7 +232,7 @@ __global__ void __launch_bounds__(256) block_stats_kernel(const uint16_t* v, con
         float total = partial[0][threadIdx.x];
 #pragma unroll
         for (int g = 1; g < 16; ++g) total = __fadd_rn(total, partial[g][threadIdx.x]);
-        const float mean = __fdiv_rn(total, static_cast<float>(count));
+        const float mean = div_full(total, static_cast<float>(count));
         mean_s[threadIdx.x] = mean;
         means[(static_cast<long long>(head) * blocks + block) * kDim + threadIdx.x] = mean;
     }
@@ -270,7 +270,7 @@ __global__ void __launch_bounds__(256) block_write_kernel(const uint16_t* k, con
 #pragma unroll
     for (int c = 0; c < 8; ++c) {
         const float a = amax[head * kDim + 8 * cg + c];
-        scale[c] = a > 0.0f ? __fdiv_rn(a, 448.0f) : 1.0f;
+        scale[c] = a > 0.0f ? div_full(a, 448.0f) : 1.0f;
         mean[c] = means[(static_cast<long long>(head) * blocks + block) * kDim + 8 * cg + c];
     }
     const long long* perm_row = perm + static_cast<long long>(head) * S;
@@ -283,7 +283,7 @@ __global__ void __launch_bounds__(256) block_write_kernel(const uint16_t* k, con
         uint32_t lo = 0, hi = 0;
 #pragma unroll
         for (int c = 0; c < 8; ++c) {
-            const float code = fminf(fmaxf(__fdiv_rn(__fsub_rn(val[i][c], mean[c]), scale[c]), -448.0f), 448.0f);
+            const float code = fminf(fmaxf(div_full(__fsub_rn(val[i][c], mean[c]), scale[c]), -448.0f), 448.0f);
             const uint32_t byte = to_e4m3(code);
             if (c < 4) lo |= byte << (8 * c);
             else hi |= byte << (8 * (c - 4));
@@ -307,7 +307,7 @@ __global__ void __launch_bounds__(256) block_write_kernel(const uint16_t* k, con
     if (rg == 0) {
 #pragma unroll
         for (int c = 0; c < 8; ++c) {
-            const __nv_bfloat16 rounded = __float2bfloat16_rn(__fdiv_rn(mean[c], scale[c]));
+            const __nv_bfloat16 rounded = __float2bfloat16_rn(div_full(mean[c], scale[c]));
             means_out[(static_cast<long long>(block) * H + head) * kDim + 8 * cg + c] = __bfloat162float(rounded);
             if (block == 0) scale_out[head * kDim + 8 * cg + c] = scale[c];
         }

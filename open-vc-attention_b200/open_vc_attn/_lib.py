@@ -25,6 +25,7 @@ SIGNATURES = {
     "ovc_prepare_fused": (_i, [_p, _p, _p, _i, _l, _l, _p, _p, _p, _p, _p, _p, _p, _p]),
     "ovc_prepare_fused_static": (_i, [_p, _p, _p, _i, _l, _l, _p, _p, _p, _p, _p, _p, _p]),
     "ovc_pack_v": (_i, [_p, _l, _l, _l, _p, _p]),
+    "ovc_div_full": (_i, [_p, _p, _p, _l, _p]),
     "ovc_repair_score": (_i, [_p, _i, _l, _l, _p, _p, _p, _p]),
     "ovc_repair_rows": (_i, [_p, _p, _p, _i, _p, _p, _p, _p, _l, _l, _l, _l, _l, _p]),
     "ovc_attention": (_i, [_p, _p, _p, _p, _l, _p, _p, _p, _l, _p, _l, _l, _l, _l, _f, _i, _p, _p]),

@@ -96,8 +96,9 @@ def _prepare(q, k, v, budget):
                                  score.data_ptr(), stream),
             "ovc_repair_score",
         )
-        # IEEE division by 448 (a tensor divisor avoids torch's multiply-by-reciprocal shortcut).
-        v_descale = amax.clamp(min=1e-12) / torch.full_like(amax, 448.0)
+        # As in the reference (v_repair.py:190): torch divides by a scalar by multiplying with its float32
+        # reciprocal, which is also what the kernels' division gives for 448.
+        v_descale = amax.clamp(min=1e-12) / 448.0
 
         layout = dict(layout)
         index = torch.topk(score, selected, dim=1, sorted=False).indices.to(torch.int32).contiguous()

@@ -50,3 +50,25 @@ def oracle_rows(prepared, m_blocks, heads, window=4, repair_kd=None):
     )
     rows = np.concatenate([np.arange(256 * m, min(256 * m + 256, q8.shape[0])) for m in m_blocks])
     return rows, out[rows]
+
+
+def hw_div(a, b):
+    """a / b evaluated by the GPU with the preparation kernels' division (ovc_div_full); float32 numpy arrays."""
+    from open_vc_attn import _lib
+
+    lib = _lib.load()
+    a = np.ascontiguousarray(a, dtype=np.float32)
+    b = np.ascontiguousarray(np.broadcast_to(np.asarray(b, dtype=np.float32), a.shape))
+    ta, tb = torch.from_numpy(a.reshape(-1)).to(DEV), torch.from_numpy(b.reshape(-1)).to(DEV)
+    tq = torch.empty_like(ta)
+    _lib.check(lib.ovc_div_full(ta.data_ptr(), tb.data_ptr(), tq.data_ptr(), ta.numel(), _lib.stream_pointer(DEV)), "ovc_div_full")
+    return tq.cpu().numpy().reshape(a.shape)
+
+
+def hw_arith():
+    """The oracle's arithmetic with the hardware's own reciprocals (see oracle/prep.py)."""
+    def recip(b):
+        b = np.asarray(b, dtype=np.float32)
+        return hw_div(np.ones_like(b), b)
+
+    return oprep.Arithmetic(recip=recip, contract=True)

@@ -10,7 +10,7 @@ from oracle import prep as oprep
 
 pytestmark = pytest.mark.gpu
 
-from gpu_util import DEV, f32, oracle_rows, structured_qkv, u8  # noqa: E402
+from gpu_util import DEV, f32, hw_arith, oracle_rows, structured_qkv, u8  # noqa: E402
 
 ORACLE_TOL = 5e-3
 
@@ -27,7 +27,8 @@ def oracle_full(q, k, v, window=4, softmax_scale=None, encoder="packed"):
     batched = qf.ndim == 4
     if not batched:
         qf, kf, vf = qf[None], kf[None], vf[None]
-    pq, pk, pv = oprep.quantize_per_block(qf), oprep.quantize_per_block(kf), oprep.quantize_per_head(vf)
+    arith = hw_arith()
+    pq, pk, pv = oprep.quantize_per_block(qf, arith), oprep.quantize_per_block(kf, arith), oprep.quantize_per_head(vf, arith)
     outs = [
         oatt.expcast_attention(pq[0][b], pk[0][b], pv[0][b], pq[1][b], pk[1][b], pv[1][b], mid_window_blocks=window,
                                softmax_scale=softmax_scale, encoder=encoder)
@@ -107,7 +108,8 @@ def test_cross_attention_and_scale():
     out = ovc.attention(q, k, v, softmax_scale=0.05)
     forward.check_status(q.device)
     qf, kf, vf = (f32(t)[None] for t in (q, k, v))
-    pq, pk, pv = oprep.quantize_per_block(qf), oprep.quantize_per_block(kf), oprep.quantize_per_head(vf)
+    arith = hw_arith()
+    pq, pk, pv = oprep.quantize_per_block(qf, arith), oprep.quantize_per_block(kf, arith), oprep.quantize_per_head(vf, arith)
     expect = oatt.expcast_attention(pq[0][0], pk[0][0], pv[0][0], pq[1][0], pk[1][0], pv[1][0], softmax_scale=0.05)
     assert oatt.relative_l2(f32(out), expect) < ORACLE_TOL
     assert oatt.relative_l2(f32(out), oatt.exact_attention(qf[0], kf[0], vf[0], softmax_scale=0.05)) < 0.10
@@ -229,9 +231,11 @@ def test_log_sum_exp_output(shape):
     heads, rows = shape[-1], shape[-2]
     assert lse.dtype == torch.float32 and tuple(lse.shape) == ((shape[0], heads, rows) if batched else (heads, rows))
     qf, kf = f32(q), f32(k)
+    arith = hw_arith()
     for b in range(shape[0] if batched else 1):
         qb, kb, vb = (f32(t)[b] if batched else f32(t) for t in (q, k, v))
-        pq, pk, pv = oprep.quantize_per_block(qb[None]), oprep.quantize_per_block(kb[None]), oprep.quantize_per_head(vb[None])
+        pq, pk, pv = (oprep.quantize_per_block(qb[None], arith), oprep.quantize_per_block(kb[None], arith),
+                      oprep.quantize_per_head(vb[None], arith))
         _, want = oatt.expcast_attention(pq[0][0], pk[0][0], pv[0][0], pq[1][0], pk[1][0], pv[1][0], return_lse=True)
         got = f32(lse)[b] if batched else f32(lse)
         assert np.abs(got - want).max() < 2e-3
@@ -254,7 +258,9 @@ def test_causal_mask(sq, sk, h):
     out, lse = ovc.attention(q, k, v, causal=True, return_lse=True)
     forward.check_status(q.device)
     assert torch.isfinite(out).all()
-    pq, pk, pv = oprep.quantize_per_block(f32(q)[None]), oprep.quantize_per_block(f32(k)[None]), oprep.quantize_per_head(f32(v)[None])
+    arith = hw_arith()
+    pq, pk, pv = (oprep.quantize_per_block(f32(q)[None], arith), oprep.quantize_per_block(f32(k)[None], arith),
+                  oprep.quantize_per_head(f32(v)[None], arith))
     want, want_lse = oatt.expcast_attention(pq[0][0], pk[0][0], pv[0][0], pq[1][0], pk[1][0], pv[1][0], mid_window_blocks=None,
                                             causal=True, return_lse=True)
     assert oatt.relative_l2(f32(out), want) < ORACLE_TOL

@@ -1,4 +1,6 @@
-"""FP8 preparation on the GPU against the CPU oracle and the reference-derived fixtures: bit-exact."""
+"""FP8 preparation on the GPU against the CPU oracle: bit-exact.  The oracle is given the GPU's own
+reciprocals (gpu_util.hw_arith), the one piece of the reference's arithmetic a CPU cannot reproduce; the
+comparison with the reference's kernels themselves is in test_gpu_prep_hw.py."""
 
 import numpy as np
 import pytest
@@ -15,36 +17,12 @@ def _imports():
     return api, preparation, quantization, v_repair
 
 
-from gpu_util import DEV, f32, packed_buffer, u8  # noqa: E402
+from gpu_util import DEV, f32, hw_arith, packed_buffer, u8  # noqa: E402
 
 
 def as_dev(bits, dtype):
     raw = torch.from_numpy(bits.view(np.int16).copy()).to(DEV)
     return raw.view(dtype)
-
-
-def test_general_quantisers_reproduce_the_reference_fixture(golden):
-    _, _, quantization, _ = _imports()
-    x = as_dev(golden["general_x_f16"], torch.float16)
-    codes, descale = quantization.fp8_quantize_per_block(x)
-    assert np.array_equal(u8(codes), golden["general_block_codes"])
-    assert np.array_equal(f32(descale), golden["general_block_descale"])
-    codes, descale = quantization.fp8_quantize_per_head(x)
-    assert np.array_equal(u8(codes), golden["general_head_codes"])
-    assert np.array_equal(f32(descale), golden["general_head_descale"])
-
-
-def test_fused_preparation_reproduces_the_reference_fixture(golden):
-    _, preparation, _, _ = _imports()
-    q, k, v = (as_dev(golden[f"fused_{n}_bf16"], torch.bfloat16) for n in "qkv")
-    p = preparation._prepare_packed(q, k, v, tuple(q.shape))
-    assert np.array_equal(u8(p.q), golden["fused_q_codes"])
-    assert np.array_equal(u8(p.k), golden["fused_k_codes"])
-    assert np.array_equal(packed_buffer(p.v), golden["fused_v_packed"])
-    assert np.array_equal(f32(p.q_descale), golden["fused_q_descale"])
-    assert np.array_equal(f32(p.k_descale), golden["fused_k_descale"])
-    assert np.array_equal(f32(p.v_descale), golden["fused_v_descale"])
-    assert p.v_prepacked and p.v.stride(0) == 1 and tuple(p.v.shape) == tuple(q.shape)
 
 
 def test_pack_v_reproduces_the_reference_fixture(golden):
@@ -72,10 +50,11 @@ def test_general_preparation_matches_the_oracle(b, s, h, dtype):
         x[-1, :, 1] = 0  # an all-zero (batch, head)
     xf = f32(x)
     codes, descale = quantization.fp8_quantize_per_block(x)
-    oc, od = oprep.quantize_per_block(xf)
+    arith = hw_arith()
+    oc, od = oprep.quantize_per_block(xf, arith)
     assert np.array_equal(u8(codes), oc) and np.array_equal(f32(descale), od)
     codes, descale = quantization.fp8_quantize_per_head(x)
-    oc, od = oprep.quantize_per_head(xf)
+    oc, od = oprep.quantize_per_head(xf, arith)
     assert np.array_equal(u8(codes), oc) and np.array_equal(f32(descale), od)
     packed = quantization.pack_v(codes)
     padded = (s + 127) // 128 * 128
@@ -112,7 +91,7 @@ def test_fused_equals_general_bytes_and_the_oracle(s, h, dtype):
     assert not buffer[:, :, s:].any()  # zero tail
     # oracle on a slice of heads (full tensors would take the CPU minutes)
     head = h - 1
-    o = oprep.prepare_fused(*[f32(t[:, head : head + 1]) for t in (q, k, v)])
+    o = oprep.prepare_fused(*[f32(t[:, head : head + 1]) for t in (q, k, v)], arith=hw_arith())
     assert np.array_equal(u8(fused.q[:, head : head + 1]), o["q"])
     assert np.array_equal(u8(fused.k[:, head : head + 1]), o["k"])
     assert np.array_equal(buffer[head : head + 1], o["v_packed"])
@@ -135,38 +114,36 @@ def test_fused_preparation_argument_errors():
         api.attention(short, short, short, preparation="fused")
 
 
-def test_repair_pieces_reproduce_the_reference_fixture(golden):
+def test_repair_pieces_match_the_oracle(golden):
     """Key copies, per-row K descales and V residual codes for a given token selection."""
     from open_vc_attn import _lib
 
     lib = _lib.load()
+    arith = hw_arith()
     v = as_dev(golden["repair_v_bf16"], torch.bfloat16)
-    k_all = torch.from_numpy(golden["repair_k_all"]).to(DEV)
+    k = as_dev(golden["repair_k_bf16"], torch.bfloat16)
+    vf, kf = f32(v), f32(k)
     s, h, rows, selected = 260, 2, 128, 5
+    o = oprep.prepare_repair(np.zeros_like(vf), kf, vf, budget=5 / 260, index=golden["repair_index"], arith=arith)
+    k_all = torch.from_numpy(o["k"].copy()).to(DEV)
     k_all[:rows] = 0
     index = torch.from_numpy(golden["repair_index"]).to(DEV)
-    amax = torch.from_numpy(golden["repair_amax"]).to(DEV)
+    amax = torch.from_numpy(oprep.head_amax(vf[None])).to(DEV)
     v_all = torch.zeros(rows + s, h, 128, dtype=torch.uint8, device=DEV)
     score = torch.empty(h, s, dtype=torch.float32, device=DEV)
     stream = _lib.stream_pointer(torch.device(DEV))
     _lib.check(lib.ovc_repair_score(v.data_ptr(), 1, s, h, amax.data_ptr(), v_all[rows:].data_ptr(), score.data_ptr(),
                                     stream), "score")
-    vf = f32(v)
-    oc, od = oprep.quantize_per_head(vf[None])
+    oc, od = oprep.quantize_per_head(vf[None], arith)
     assert np.array_equal(v_all[rows:].cpu().numpy(), oc[0])
-    expect_score = oprep.v_residual_score(vf, oc[0], od[0])
-    assert np.allclose(f32(score), expect_score, rtol=1e-5, atol=0)
-    ok = golden["repair_score_row_ok"].T
-    assert np.allclose(f32(score)[ok], golden["repair_score"][ok], rtol=1e-5, atol=0)
-    k_descale = torch.from_numpy(oprep.quantize_per_block(f32(as_dev(golden["repair_k_bf16"], torch.bfloat16))[None])[1]).to(DEV)
-    v_descale = torch.from_numpy(golden["repair_v_descale"]).to(DEV)
+    assert np.allclose(f32(score), o["score"], rtol=1e-5, atol=0)
+    k_descale = torch.from_numpy(oprep.quantize_per_block(kf[None], arith)[1]).to(DEV)
+    v_descale = torch.from_numpy(od).to(DEV)
     repair_kd = torch.empty(1, h, rows, dtype=torch.float32, device=DEV)
     _lib.check(lib.ovc_repair_rows(k_all.data_ptr(), v_all.data_ptr(), v.data_ptr(), 1, k_descale.data_ptr(),
                                    v_descale.data_ptr(), index.data_ptr(), repair_kd.data_ptr(), selected, rows, s, h,
                                    3, stream), "rows")
-    assert np.array_equal(k_all.cpu().numpy(), golden["repair_k_all"])
-    assert np.array_equal(f32(repair_kd), golden["repair_kd"])
-    o = oprep.prepare_repair(np.zeros_like(vf), f32(as_dev(golden["repair_k_bf16"], torch.bfloat16)), vf,
-                             budget=5 / 260, index=golden["repair_index"])
+    assert np.array_equal(k_all.cpu().numpy(), o["k"])
+    assert np.array_equal(f32(repair_kd), o["repair_k_descale"])
     expect_v = o["v_packed"][:, :, : rows + s].transpose(2, 0, 1)
     assert np.array_equal(v_all.cpu().numpy(), expect_v)

@@ -11,7 +11,7 @@ from oracle import prep as oprep
 
 pytestmark = pytest.mark.gpu
 
-from gpu_util import DEV, f32, oracle_rows, packed_buffer, u8  # noqa: E402
+from gpu_util import DEV, f32, hw_arith, oracle_rows, packed_buffer, u8  # noqa: E402
 
 
 def _mods():
@@ -94,8 +94,9 @@ def test_repair_prefix_contents_against_the_oracle():
     selected, rows = prepared.selected_tokens, prepared.repair_tokens
     assert (selected, rows) == (30, 128)
     vf, kf, qf = f32(v), f32(k), f32(q)
-    oc, od = oprep.quantize_per_head(vf[None])
-    score = oprep.v_residual_score(vf, oc[0], od[0])
+    arith = hw_arith()
+    oc, od = oprep.quantize_per_head(vf[None], arith)
+    score = oprep.v_residual_score(vf, oc[0], od[0], arith)
     k8 = u8(prepared.k)
     index = np.zeros((h, selected), dtype=np.int64)
     for head in range(h):
@@ -105,7 +106,7 @@ def test_repair_prefix_contents_against_the_oracle():
             assert matches, "repair key is not one of the top-scoring tokens"
             index[head, r] = matches[0]
         assert len(set(index[head].tolist())) == selected
-    o = oprep.prepare_repair(qf, kf, vf, budget=0.03, index=index)
+    o = oprep.prepare_repair(qf, kf, vf, budget=0.03, index=index, arith=arith)
     assert np.array_equal(u8(prepared.q), o["q"])
     assert np.array_equal(k8, o["k"])
     assert np.array_equal(packed_buffer(prepared.v), o["v_packed"])

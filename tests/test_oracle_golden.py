@@ -1,5 +1,9 @@
-"""The CPU oracle against fixtures produced by the reference's own Triton kernels
-(tests/golden/make_golden.py) and against the worked examples of its report."""
+"""The CPU oracle against fixtures produced by the reference's own Triton kernels and against the worked
+examples of its report.  Two fixture files pin the preparation: prep_golden.npz (tests/golden/make_golden.py,
+Triton's CPU interpreter: IEEE division) and prep_golden_gpu.npz (tests/golden/make_golden_gpu.py, the same
+kernels on a B200: the GPU's division, whose reciprocals are stored with the fixture)."""
+
+import os
 
 import numpy as np
 import pytest
@@ -35,11 +39,11 @@ def test_e4m3_matches_torch_cast():
 
 def test_general_quantisers_match_reference(golden):
     x = f16(golden["general_x_f16"])
-    codes, descale = prep.quantize_per_block(x)
+    codes, descale = prep.quantize_per_block(x, prep.IEEE)
     assert np.array_equal(codes, golden["general_block_codes"])
     assert np.array_equal(descale, golden["general_block_descale"])
     assert np.array_equal(prep.head_amax(x), golden["general_head_amax"])
-    codes, descale = prep.quantize_per_head(x)
+    codes, descale = prep.quantize_per_head(x, prep.IEEE)
     assert np.array_equal(codes, golden["general_head_codes"])
     assert np.array_equal(descale, golden["general_head_descale"])
     # the all-zero (batch, head): codes 0 and the floored scale
@@ -48,7 +52,7 @@ def test_general_quantisers_match_reference(golden):
 
 def test_fused_preparation_matches_reference(golden):
     q, k, v = (bf16(golden[f"fused_{n}_bf16"]) for n in "qkv")
-    out = prep.prepare_fused(q, k, v)
+    out = prep.prepare_fused(q, k, v, prep.IEEE)
     assert not golden["fused_amax_after_init"].any()
     assert np.array_equal(out["q"], golden["fused_q_codes"])
     assert np.array_equal(out["k"], golden["fused_k_codes"])
@@ -67,7 +71,7 @@ def test_pack_v_matches_reference(golden):
 def test_repair_pieces_match_reference(golden):
     v, k = bf16(golden["repair_v_bf16"]), bf16(golden["repair_k_bf16"])
     index = golden["repair_index"]
-    out = prep.prepare_repair(np.zeros_like(k), k, v, budget=5 / 260, index=index)
+    out = prep.prepare_repair(np.zeros_like(k), k, v, budget=5 / 260, index=index, arith=prep.IEEE)
     assert (out["selected_tokens"], out["repair_tokens"], out["total"]) == (5, 128, 388)
     assert np.array_equal(out["k"], golden["repair_k_all"])
     assert np.array_equal(out["repair_k_descale"], golden["repair_kd"])
@@ -82,6 +86,72 @@ def test_repair_pieces_match_reference(golden):
     theirs = golden["repair_v_prefix_interp"]
     assert not mine[5:].any() and not theirs[5:].any()
     assert (mine[:5] == theirs[:5]).mean() > 0.9
+
+
+@pytest.fixture(scope="module")
+def hw():
+    return np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "prep_golden_gpu.npz"))
+
+
+def hw_arith(hw):
+    return prep.Arithmetic(recip=prep.RecipTable(hw["rcp_b"], hw["rcp_r"]), contract=True)
+
+
+def test_gpu_division_model(hw):
+    """a / b on the GPU is the dividend times the recorded reciprocal, rounded once; the reciprocal of 448
+    is the correctly rounded one, other reciprocals differ from RN(1/b) in the last bit now and then."""
+    assert int(hw["div_model_violations"]) == 0
+    table = prep.RecipTable(hw["rcp_b"], hw["rcp_r"])
+    assert table(np.float32([448.0]))[0] == np.float32(1.0) / np.float32(448.0)
+    off = (prep.recip_model(hw["rcp_b"]) != hw["rcp_r"]).mean()
+    assert 0.0 < off < 0.5
+
+
+def test_general_quantisers_match_the_reference_on_hardware(golden, hw):
+    x = f16(golden["general_x_f16"])
+    arith = hw_arith(hw)
+    codes, descale = prep.quantize_per_block(x, arith)
+    assert np.array_equal(codes, hw["hw_general_block_codes"])
+    assert np.array_equal(descale, hw["hw_general_block_descale"])
+    codes, descale = prep.quantize_per_head(x, arith)
+    assert np.array_equal(codes, hw["hw_general_head_codes"])
+    assert np.array_equal(descale, hw["hw_general_head_descale"])
+
+
+def test_fused_preparation_matches_the_reference_on_hardware(golden, hw):
+    q, k, v = (bf16(golden[f"fused_{n}_bf16"]) for n in "qkv")
+    out = prep.prepare_fused(q, k, v, hw_arith(hw))
+    for name in ("q", "k"):
+        assert np.array_equal(out[name], hw[f"hw_fused_{name}_codes"]), name
+        assert np.array_equal(out[name + "_descale"], hw[f"hw_fused_{name}_descale"]), name
+    assert np.array_equal(out["v_packed"], hw["hw_fused_v_packed"])
+    assert np.array_equal(out["v_descale"], hw["hw_fused_v_descale"])
+
+
+def test_config_c1_matches_the_reference_on_hardware(hw):
+    """BASELINE configuration 1: Q, K, V [1024, 2, 128] BF16, N(0,1), seed 0."""
+    torch = pytest.importorskip("torch")
+    torch.manual_seed(0)
+    q, k, v = [torch.randn(1024, 2, 128).to(torch.bfloat16).float().numpy() for _ in range(3)]
+    out = prep.prepare_fused(q, k, v, hw_arith(hw))
+    assert np.array_equal(out["q"], hw["c1_fused_q_codes"]) and np.array_equal(out["q"], hw["c1_q_codes"])
+    assert np.array_equal(out["k"], hw["c1_fused_k_codes"]) and np.array_equal(out["k"], hw["c1_k_codes"])
+    assert np.array_equal(out["v_packed"], hw["c1_fused_v_packed"])
+    assert np.array_equal(out["q_descale"], hw["c1_fused_q_descale"])
+    assert np.array_equal(out["k_descale"], hw["c1_fused_k_descale"]) and np.array_equal(out["k_descale"], hw["c1_k_descale"])
+    assert np.array_equal(out["v_descale"], hw["c1_fused_v_descale"]) and np.array_equal(out["v_descale"], hw["c1_v_descale"])
+
+
+def test_repair_pieces_match_the_reference_on_hardware(golden, hw):
+    v, k = bf16(golden["repair_v_bf16"]), bf16(golden["repair_k_bf16"])
+    out = prep.prepare_repair(np.zeros_like(k), k, v, budget=5 / 260, index=golden["repair_index"], arith=hw_arith(hw))
+    assert np.array_equal(out["k"], hw["hw_repair_k_all"])
+    assert np.array_equal(out["repair_k_descale"], hw["hw_repair_kd"])
+    assert np.array_equal(out["v_descale"], hw["hw_repair_v_descale"])
+    v_all = out["v_packed"][:, :, : out["total"]].transpose(2, 0, 1)
+    assert np.array_equal(v_all[128:], hw["hw_repair_v_codes"])
+    assert np.array_equal(v_all[:128], hw["hw_repair_v_prefix"])
+    assert np.allclose(out["score"], hw["hw_repair_score"], rtol=2e-6, atol=0)
 
 
 def test_repair_counts_follow_the_reference_examples():
