@@ -41,7 +41,7 @@ extern "C" {
 #define OVC_ERR_TOO_LARGE (-5)   /* a size exceeds what the library's built-in scratch memory can hold */
 
 /* Bits of the device status word written by ovc_attention (0 = clean run). */
-#define OVC_STATUS_WAIT_EXPIRED 1u /* a bounded barrier wait gave up; the output is invalid */
+#define OVC_STATUS_WAIT_EXPIRED 1u /* a bounded barrier wait gave up; the output rows of that launch hold NaN */
 
 int ovc_version(void);
 const char* ovc_error_string(int code);
@@ -164,14 +164,27 @@ int ovc_repair_rows(void* k_all, void* v_all, const void* v_src, int dtype, cons
  *   softmax_scale   > 0 and finite
  *   mid_window_blocks  >= 0: start the key scan that many 128-key blocks right of the diagonal;
  *                      -1: plain right-to-left scan
- *   status      one uint32 in device memory, OR-ed with OVC_STATUS_* bits by the kernel; the caller
- *               clears it and reads it back when it wants to check.  May be NULL.
- * Creates its tensor maps on the host with the driver's cuTensorMapEncodeTiled; no device allocation.
+ *   status      two uint32 in device memory, or NULL.  Every wait inside the kernel is bounded (about
+ *               0.2 s).  A CTA whose wait expires ORs OVC_STATUS_* bits into both words, fills the output
+ *               rows it owns with NaN (-inf in lse) and exits; CTAs of the same launch that start
+ *               afterwards do the same without computing.  status[0] is this launch's word: the entry
+ *               point clears it (stream-ordered) before the launch, so an expiry never leaks into later
+ *               calls.  status[1] is sticky: the library only ever sets bits in it, the caller reads and
+ *               clears it when it wants to know whether any launch since the last look gave up.
  */
 int ovc_attention(const void* q8, const void* k8, const void* v_packed, const float* q_descale,
                   int64_t q_blocks, const float* k_descale, const float* v_descale, const float* repair_kd,
                   int64_t repair_rows, void* out, int64_t B, int64_t Sq, int64_t Sk, int64_t H,
                   float softmax_scale, int mid_window_blocks, uint32_t* status, void* stream);
+
+/*
+ * Runs the kernels' bounded barrier wait on its own: one 64-thread CTA waits at most `limit_cycles` clock
+ * ticks on a barrier that cannot complete, then sets OVC_STATUS_WAIT_EXPIRED in status[0] and status[1] (the
+ * two words ovc_attention takes) and adds the number of threads that gave up to *gave_up (device memory).  No tensor-core work or copy is in flight, the
+ * context stays usable.  For tests of the failure path; has no counterpart in the reference, whose waits are
+ * unbounded (cute/blackwell_helpers.py:538-545).
+ */
+int ovc_selftest_wait(uint32_t* status, int64_t limit_cycles, uint32_t* gave_up, void* stream);
 
 /*
  * Copies `heads` consecutive heads of a [S, src_heads, bytes_per_head] tensor into a

@@ -27,16 +27,14 @@
 // O0 192..327, O1 328..463; each O region is 128 output columns followed by 8 copies of the
 // denominator (the PV product has N = 136).
 
+#include <atomic>
+
 #include <cuda.h>
 #include <cuda_bf16.h>
 #include <math.h>
 
 #include "common.cuh"
 #include "sm100_ptx.cuh"
-
-#ifndef OVC_MAX3
-#define OVC_MAX3 1
-#endif
 
 namespace ovc {
 namespace {
@@ -95,16 +93,20 @@ __device__ __forceinline__ int tile_at(int it, int j0, int first_tile, int n_til
     return first_tile - 1 - (it - originals);
 }
 
-__device__ __forceinline__ void give_up(SmemLayout& sm, uint32_t* status) {
-    sm.abort_flag = 1;
-    if (status != nullptr) atomicOr(status, OVC_STATUS_WAIT_EXPIRED);
+__device__ __forceinline__ void give_up(volatile uint32_t* abort_flag, uint32_t* status) {
+    *abort_flag = 1;
+    if (status != nullptr) {
+        atomicOr(status, OVC_STATUS_WAIT_EXPIRED);      // this launch: later CTAs do not start
+        atomicOr(status + 1, OVC_STATUS_WAIT_EXPIRED);  // sticky: for the host to read and clear
+    }
 }
 
 // Bounded wait.  The hardware suspends the thread inside try_wait while the phase is pending, so a
 // waiting warp issues almost nothing; the abort flag and the clock are looked at only every 16th
 // wake-up.  Returns false when the barrier did not complete in time or another thread of the CTA
 // already gave up; the caller then leaves its loop and the CTA tears down.
-__device__ __forceinline__ bool wait_bar(SmemLayout& sm, uint64_t* bar, uint32_t parity, uint32_t* status) {
+__device__ __forceinline__ bool wait_bar(volatile uint32_t* abort_flag, uint64_t* bar, uint32_t parity, uint32_t* status,
+                                         long long limit) {
     const uint32_t addr = smem_addr(bar);
     if (mbar_try_wait(addr, parity)) return true;
     long long start = 0;
@@ -112,15 +114,19 @@ __device__ __forceinline__ bool wait_bar(SmemLayout& sm, uint64_t* bar, uint32_t
     for (uint32_t tries = 1;; ++tries) {
         if (mbar_try_wait_sleep(addr, parity, kSleepHintNs)) return true;
         if ((tries & 15u) == 0) {
-            if (sm.abort_flag) return false;
+            if (*abort_flag) return false;
             const long long now = clock64();
             if (start == 0) start = now;
-            if (now - start > kWaitCycles) {
-                give_up(sm, status);
+            if (now - start > limit) {
+                give_up(abort_flag, status);
                 return false;
             }
         }
     }
+}
+
+__device__ __forceinline__ bool wait_bar(SmemLayout& sm, uint64_t* bar, uint32_t parity, uint32_t* status) {
+    return wait_bar(&sm.abort_flag, bar, parity, status, kWaitCycles);
 }
 
 // The MMA warp's reaction time is on the critical path of the shared score buffer, and it shares its
@@ -147,23 +153,6 @@ __device__ __forceinline__ void qk_issue(uint32_t d_tmem, const uint64_t (&da)[4
           "r"(idesc), "r"(bar)
         : "memory");
 }
-
-#ifdef OVC_DEBUG_DUMP
-// Debug builds only: raw scores and codes of CTA 0's first key tile go to this buffer.
-__device__ float* g_debug_dump = nullptr;
-// Timeline stamps (%clock) of CTA 0's first 64 steps: [step][32 slots]; tl_base is a register copy
-// of the buffer pointer so that a stamp costs one special-register read and one store.
-#define OVC_TL(step, slot)                                                                  \
-    do {                                                                                    \
-        if (tl_base != nullptr && (step) >= 256 && (step) < 320 && lane == 0) {             \
-            uint32_t now;                                                                   \
-            asm volatile("mov.u32 %0, %%clock;" : "=r"(now));                               \
-            tl_base[((step) - 256) * 32 + (slot)] = now;                                    \
-        }                                                                                   \
-    } while (0)
-#else
-#define OVC_TL(step, slot) do {} while (0)
-#endif
 
 __device__ __forceinline__ float fmax3(float a, float b, float c) {
     float d;
@@ -226,9 +215,8 @@ __device__ __forceinline__ void encode128(const uint32_t (&s)[128], uint64_t sca
     }
 }
 
-// Row max of 128 scores: three-input max tree (64 instructions); OVC_MAX3=0 selects a two-input tree.
+// Row max of 128 scores: three-input max tree (64 instructions).
 __device__ __forceinline__ float max128(const uint32_t (&s)[128]) {
-#if OVC_MAX3
     float m9[43];
 #pragma unroll
     for (int c = 0; c < 42; ++c)
@@ -242,16 +230,6 @@ __device__ __forceinline__ float max128(const uint32_t (&s)[128]) {
 #pragma unroll
     for (int c = 0; c < 5; ++c) m1[c] = fmax3(m3[3 * c], m3[3 * c + 1], m3[3 * c + 2]);
     return fmaxf(fmax3(m1[0], m1[1], m1[2]), fmaxf(m1[3], m1[4]));
-#else
-    float m[64];
-#pragma unroll
-    for (int i = 0; i < 64; ++i) m[i] = fmaxf(__uint_as_float(s[i]), __uint_as_float(s[i + 64]));
-#pragma unroll
-    for (int w = 32; w > 0; w >>= 1)
-#pragma unroll
-        for (int i = 0; i < w; ++i) m[i] = fmaxf(m[i], m[i + w]);
-    return m[0];
-#endif
 }
 
 __device__ __forceinline__ uint32_t bf16x2(float lo, float hi) {
@@ -267,6 +245,18 @@ __device__ __forceinline__ void drain_mmas(SmemLayout& sm, int which) {
     while (!mbar_try_wait(smem_addr(&sm.drain[which]), 0) && clock64() - t0 < kWaitCycles) {}
 }
 
+// A launch that gave up (or found the status word already set) leaves NaN in the rows it owns, and -inf
+// in their log-sum-exp, so that a caller that never reads the status word cannot mistake the buffer for a
+// result.
+__device__ __forceinline__ void poison_row(const AttnParams& p, int batch, int head, long long row) {
+    if (row >= p.Sq) return;
+    uint4* dst = reinterpret_cast<uint4*>(p.out + ((static_cast<long long>(batch) * p.Sq + row) * p.H + head) * kDim);
+    const uint4 nan4 = make_uint4(0x7FC07FC0u, 0x7FC07FC0u, 0x7FC07FC0u, 0x7FC07FC0u);
+#pragma unroll
+    for (int i = 0; i < 16; ++i) dst[i] = nan4;
+    if (p.lse != nullptr) p.lse[(static_cast<long long>(batch) * p.H + head) * p.Sq + row] = -INFINITY;
+}
+
 // kVS: V-Smooth variant (VC-Attention baseline): V holds residual codes; every key step adds
 // (sum of the tile's probabilities) x (the tile's block mean) to the accumulator, and the output is
 // scaled per channel (cute/flash_fwd_sm100.py:4857-4863 of the reference).
@@ -277,21 +267,20 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
     extern __shared__ uint8_t smem_raw[];
     SmemLayout& sm = *reinterpret_cast<SmemLayout*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
 
-    // A barrier wait already expired in this launch: do not start more work.  One thread reads the
-    // word so that the whole CTA takes the same decision.
-    __shared__ uint32_t skip_cta;
-    if (threadIdx.x == 0) skip_cta = p.status != nullptr ? *reinterpret_cast<volatile uint32_t*>(p.status) : 0u;
-    __syncthreads();
-    if (skip_cta != 0) return;
-
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-#ifdef OVC_DEBUG_DUMP
-    uint32_t* const tl_base = (g_debug_dump != nullptr && blockIdx.x == 0)
-                                  ? reinterpret_cast<uint32_t*>(g_debug_dump) + 256 * 128 + 256 * 32 : nullptr;
-#endif
     const int m_block = blockIdx.x % p.m_blocks;
     const int bh = blockIdx.x / p.m_blocks;
     const int head = bh % p.H, batch = bh / p.H;
+
+    // A barrier wait already expired in this launch (the entry point clears the word before the launch): do
+    // not start more work.  One thread reads the word so that the whole CTA takes the same decision.
+    __shared__ uint32_t skip_cta;
+    if (threadIdx.x == 0) skip_cta = p.status != nullptr ? *reinterpret_cast<volatile uint32_t*>(p.status) : 0u;
+    __syncthreads();
+    if (skip_cta != 0) {
+        if (threadIdx.x < 2 * kTile) poison_row(p, batch, head, static_cast<long long>(m_block) * (2 * kTile) + threadIdx.x);
+        return;
+    }
     // Causal (bottom-right aligned, cute/mask.py:186-199): key column c is visible to query row r iff
     // c < r + 1 + Sk - Sq, so this CTA's rows need the tiles below `visible` only (at least one tile is
     // visited: fully masked rows then end with a zero denominator and produce zeros).
@@ -414,9 +403,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
             // gate[s] completion n: stage s has copied S_s(n) out, so the score buffer is free for the other
             // stage's next step (stage 1: step n, stage 0: step n + 1).
             for (int n = 0; ok && n < n_iters; ++n) {
-                [[maybe_unused]] const int it = n;  // step index for debug stamps
                 for (int s = 0; s < 2; ++s) {
-                    OVC_TL(it, 12 + s * 6 + 0);
                     const int qk_step = n + s;
                     if (qk_step >= n_iters) break;
                     const uint32_t a_lo = smem_desc_lo(smem_addr(sm.q[1 - s]));
@@ -426,9 +413,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
                     const uint32_t score_bar = smem_addr(&sm.s_full[1 - s]);
                     ok = __all_sync(0xFFFFFFFFu, wait_bar(sm, &sm.gate[s], n & 1, p.status));
                     if (!ok) break;
-                    OVC_TL(it, 12 + s * 6 + 1);
                     qk_issue(tmem + kColS, da, db, idesc_qk, score_bar);
-                    OVC_TL(it, 12 + s * 6 + 2);
                 }
             }
             if (!ok) drain_mmas(sm, 0);
@@ -489,10 +474,8 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         for (int it = 0; it < n_iters; ++it) {
             const int j = tile_at(it, j0, p.first_tile, n_tiles);
             const float kd = __ldg(kd_row + j);
-            if ((warp & 3) == 0) OVC_TL(it, stage * 6 + 0);
             ok = __all_sync(0xFFFFFFFFu, wait_bar(sm, &sm.s_full[stage], it & 1, p.status));
             if (!ok) break;
-            if ((warp & 3) == 0) OVC_TL(it, stage * 6 + 1);
             tc_fence_after();
             if (warp == 4 && lane == 0) mbar_arrive(smem_addr(&sm.k_empty[it % kKStages]));  // K(it) has been read
             uint32_t s[128];
@@ -503,14 +486,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
             tmem_wait_ld();
             tc_fence_before();
             mbar_arrive(my_gate);
-            if ((warp & 3) == 0) OVC_TL(it, stage * 6 + 2);
 
-#ifdef OVC_DEBUG_DUMP
-            if (g_debug_dump != nullptr && blockIdx.x == 0 && it == 0) {
-                float* d = g_debug_dump + (stage * 128 + row_in_tile) * 128;
-                for (int c = 0; c < 128; ++c) d[c] = __uint_as_float(s[c]);
-            }
-#endif
             if (j == p.n_tiles - 1 && tail_valid < kTile) {
 #pragma unroll
                 for (int c = 0; c < 128; ++c)
@@ -544,7 +520,6 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
             const float code_scale = code_scale0 * kd;
             const uint64_t scale2 = pack2(code_scale, code_scale);
             const float tile_max = max128(s) * kd;
-            if ((warp & 3) == 0) OVC_TL(it, stage * 6 + 3);
             float alpha = 1.0f;
             if (it == 0 || tile_max > row_max) {
                 float new_max = tile_max;
@@ -568,13 +543,6 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
                 if (warp == 4 && lane == 0) mbar_arrive(smem_addr(&sm.v_empty[(it - 1) % kVStages]));  // V(it-1) has been read
             }
             tmem_st32(t_p, codes);
-            if ((warp & 3) == 0) OVC_TL(it, stage * 6 + 4);
-#ifdef OVC_DEBUG_DUMP
-            if (g_debug_dump != nullptr && blockIdx.x == 0 && it == 0) {
-                uint32_t* d = reinterpret_cast<uint32_t*>(g_debug_dump) + 256 * 128 + (stage * 128 + row_in_tile) * 32;
-                for (int c = 0; c < 32; ++c) d[c] = codes[c];
-            }
-#endif
 
             if (kVS) {
                 if (it > 0) {
@@ -631,7 +599,6 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
             tmem_wait_st();
             tc_fence_before();
             mbar_arrive(smem_addr(&sm.p_full[stage]));  // P_s(it) stored, O_s rescaled
-            if ((warp & 3) == 0) OVC_TL(it, stage * 6 + 5);
         }
         if (ok) ok = __all_sync(0xFFFFFFFFu, wait_bar(sm, &sm.o_full[stage], 0, p.status));
         if (ok) {
@@ -678,6 +645,8 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
                     }
                 }
             }
+        } else {
+            poison_row(p, batch, head, static_cast<long long>(q_tile) * kTile + row_in_tile);
         }
     }
     tc_fence_before();
@@ -686,6 +655,23 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         tc_fence_after();
         tmem_dealloc(tmem, kTmemCols);
     }
+}
+
+// The bounded wait on its own: one small CTA waits, with a caller-given limit, on a barrier that is one
+// arrival short of its count and so can never complete.  Nothing else is in flight (no TMA, no MMA, no tensor
+// memory), so giving up is the whole story: the status bit is set, the wait returns false and the CTA exits.
+__global__ void __launch_bounds__(64, 1) wait_selftest_kernel(uint32_t* status, long long limit, uint32_t* gave_up) {
+    __shared__ alignas(8) uint64_t barrier;
+    __shared__ volatile uint32_t abort_flag;
+    if (threadIdx.x == 0) {
+        mbar_init(smem_addr(&barrier), 2);
+        abort_flag = 0;
+        mbar_init_fence();
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) mbar_arrive(smem_addr(&barrier));  // one of the two arrivals; the other never comes
+    const bool completed = wait_bar(&abort_flag, &barrier, 0, status, limit);
+    if (!completed) atomicAdd(gave_up, 1u);
 }
 
 // ---- host side -------------------------------------------------------------------------------
@@ -729,12 +715,6 @@ int make_map(CUtensorMap* map, const void* base, const cuuint64_t (&dims)[4], co
 
 using namespace ovc;
 
-#ifdef OVC_DEBUG_DUMP
-extern "C" int ovc_debug_set_dump(float* buffer) {
-    return cudaMemcpyToSymbol(g_debug_dump, &buffer, sizeof(buffer)) == cudaSuccess ? 0 : -2;
-}
-#endif
-
 namespace {
 
 int launch_attention(const void* q8, const void* k8, const void* v_packed, const float* q_descale, int64_t q_blocks,
@@ -755,10 +735,11 @@ int launch_attention(const void* q8, const void* k8, const void* v_packed, const
 
     int device = 0;
     cudaError_t err = cudaGetDevice(&device);
-    int major = 0;
+    int major = 0, minor = 0;
     if (err == cudaSuccess) err = cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, device);
+    if (err == cudaSuccess) err = cudaDeviceGetAttribute(&minor, cudaDevAttrComputeCapabilityMinor, device);
     if (err != cudaSuccess) { set_last_cuda_error(err); return OVC_ERR_CUDA; }
-    if (major != 10) return OVC_ERR_UNSUPPORTED;
+    if (major != 10 || minor != 0) return OVC_ERR_UNSUPPORTED;  // the library holds sm_100a code only
 
     CUtensorMap map_q, map_k, map_v;
     {
@@ -789,18 +770,23 @@ int launch_attention(const void* q8, const void* k8, const void* v_packed, const
     p.scale_log2 = static_cast<float>(static_cast<double>(softmax_scale) * 1.4426950408889634);
 
     const size_t smem_bytes = sizeof(SmemLayout) + 1024;
-    static bool configured[64] = {};
-    if (device < 64 && !configured[device]) {
+    static std::atomic<bool> configured[64];
+    if (device < 64 && !configured[device].load(std::memory_order_acquire)) {
         err = cudaFuncSetAttribute(attention_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem_bytes));
         if (err == cudaSuccess)
             err = cudaFuncSetAttribute(attention_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem_bytes));
         if (err == cudaSuccess)
             err = cudaFuncSetAttribute(attention_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem_bytes));
         if (err != cudaSuccess) { set_last_cuda_error(err); return OVC_ERR_CUDA; }
-        configured[device] = true;
+        configured[device].store(true, std::memory_order_release);
     }
     const unsigned grid = static_cast<unsigned>(m_blocks * H * B);
     auto s = static_cast<cudaStream_t>(stream);
+    if (status != nullptr) {
+        // status[0] belongs to this launch alone: an expiry in an earlier call must not stop this one.
+        err = cudaMemsetAsync(status, 0, sizeof(uint32_t), s);
+        if (err != cudaSuccess) { set_last_cuda_error(err); return OVC_ERR_CUDA; }
+    }
     if (vs_means != nullptr) attention_kernel<true, false><<<grid, kThreads, smem_bytes, s>>>(map_q, map_k, map_v, p);
     else if (causal) attention_kernel<false, true><<<grid, kThreads, smem_bytes, s>>>(map_q, map_k, map_v, p);
     else attention_kernel<false, false><<<grid, kThreads, smem_bytes, s>>>(map_q, map_k, map_v, p);
@@ -808,6 +794,12 @@ int launch_attention(const void* q8, const void* k8, const void* v_packed, const
 }
 
 }  // namespace
+
+extern "C" int ovc_selftest_wait(uint32_t* status, int64_t limit_cycles, uint32_t* gave_up, void* stream) {
+    if (!status || !gave_up || limit_cycles < 1 || limit_cycles > (1LL << 32)) return OVC_ERR_ARGUMENT;
+    wait_selftest_kernel<<<1, 64, 0, static_cast<cudaStream_t>(stream)>>>(status, limit_cycles, gave_up);
+    return check_launch();
+}
 
 extern "C" int ovc_attention(const void* q8, const void* k8, const void* v_packed, const float* q_descale,
                              int64_t q_blocks, const float* k_descale, const float* v_descale, const float* repair_kd,

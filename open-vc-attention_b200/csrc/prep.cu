@@ -15,6 +15,8 @@
 #include <cuda_fp16.h>
 #include <cuda_fp8.h>
 
+#include <atomic>
+
 #include "common.cuh"
 
 namespace ovc {
@@ -424,7 +426,8 @@ static __device__ __align__(256) float g_static_amax[OVC_STATIC_MAX_HEADS];
 namespace {
 
 constexpr int kMaxDevices = 64;
-float* g_static_amax_ptr[kMaxDevices] = {};
+// Filled on the first call per device; atomic so that host threads making that first call together agree.
+std::atomic<float*> g_static_amax_ptr[kMaxDevices];
 
 // Device address of g_static_amax on the current device (looked up on the first call per device).
 int static_amax_pointer(float** out) {
@@ -435,16 +438,16 @@ int static_amax_pointer(float** out) {
         return OVC_ERR_CUDA;
     }
     if (device < 0 || device >= kMaxDevices) return OVC_ERR_ARGUMENT;
-    if (g_static_amax_ptr[device] == nullptr) {
-        float* ptr = nullptr;
+    float* ptr = g_static_amax_ptr[device].load(std::memory_order_acquire);
+    if (ptr == nullptr) {
         err = cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_static_amax);
         if (err != cudaSuccess || ptr == nullptr) {
             set_last_cuda_error(err);
             return OVC_ERR_CUDA;
         }
-        g_static_amax_ptr[device] = ptr;
+        g_static_amax_ptr[device].store(ptr, std::memory_order_release);
     }
-    *out = g_static_amax_ptr[device];
+    *out = ptr;
     return OVC_OK;
 }
 

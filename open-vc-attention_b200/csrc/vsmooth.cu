@@ -385,7 +385,9 @@ int ovc_vs_update_centers(const float* sums, const float* counts, void* centers,
 
 int ovc_vs_block_stats(const void* v, const int64_t* permutation, float* means, float* amax, int64_t S, int64_t H,
                        void* stream) {
-    if (!v || !permutation || !means || !amax || bad(S, H, 1)) return OVC_ERR_ARGUMENT;
+    if (!v || !permutation || !means || !amax || bad(S, H, 1) || !aligned16(v) ||
+        (reinterpret_cast<uintptr_t>(permutation) & 7u))
+        return OVC_ERR_ARGUMENT;
     auto s = static_cast<cudaStream_t>(stream);
     cudaError_t err = cudaMemsetAsync(amax, 0, sizeof(float) * H * kDim, s);
     if (err != cudaSuccess) { set_last_cuda_error(err); return OVC_ERR_CUDA; }
@@ -398,7 +400,9 @@ int ovc_vs_block_stats(const void* v, const int64_t* permutation, float* means, 
 
 int ovc_vs_block_write(const void* k, const void* v, const int64_t* permutation, const float* means, const float* amax,
                        void* k_out, void* codes, float* means_out, float* scale, int64_t S, int64_t H, void* stream) {
-    if (!k || !v || !permutation || !means || !amax || !k_out || !codes || !means_out || !scale || bad(S, H, 1))
+    if (!k || !v || !permutation || !means || !amax || !k_out || !codes || !means_out || !scale || bad(S, H, 1) ||
+        !aligned16(k) || !aligned16(v) || (reinterpret_cast<uintptr_t>(permutation) & 7u) ||
+        (reinterpret_cast<uintptr_t>(k_out) & 7u) || (reinterpret_cast<uintptr_t>(codes) & 7u))
         return OVC_ERR_ARGUMENT;
     const int blocks = static_cast<int>(ceil_div(S, kTile));
     block_write_kernel<<<dim3(blocks, static_cast<unsigned>(H)), 256, 0, static_cast<cudaStream_t>(stream)>>>(

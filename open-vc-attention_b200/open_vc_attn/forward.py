@@ -17,20 +17,54 @@ _status_words = {}
 
 
 def status_word(device):
-    """One sticky uint32 per device that the kernel ORs error bits into."""
+    """Two uint32 per device for the kernel: [0] the current launch's word (cleared by the library before each
+    launch), [1] sticky, OR-ed by any launch whose bounded wait expired."""
+    return _status(device)[0]
+
+
+def _status(device):
     key = torch.device(device).index
+    if key is None:
+        key = torch.cuda.current_device()
     if key not in _status_words:
-        _status_words[key] = torch.zeros(1, dtype=torch.int32, device=device)
+        words = torch.zeros(2, dtype=torch.int32, device=torch.device("cuda", key))
+        mirror = torch.zeros(1, dtype=torch.int32).pin_memory()  # host copy of words[1], refreshed after every launch
+        _status_words[key] = (words, mirror)
     return _status_words[key]
 
 
-def check_status(device):
-    """Synchronise and raise if any attention launch on ``device`` gave up on a barrier wait."""
-    word = status_word(device)
-    value = int(word.item())
+def _failure(value):
+    return RuntimeError(
+        f"open_vc_attn attention kernel reported status {value:#x} (a bounded wait expired); "
+        "the output of that call holds NaN"
+    )
+
+
+def _raise_if_flagged(device):
+    """No synchronisation: looks at the host copy of the sticky word, which reflects every launch whose
+    trailing 4-byte copy has completed.  Called at the start of each public attention call."""
+    words, mirror = _status(device)
+    value = int(mirror[0])
     if value != 0:
-        word.zero_()
-        raise RuntimeError(f"open_vc_attn attention kernel reported status {value:#x} (bounded wait expired)")
+        mirror.zero_()
+        words[1:].zero_()
+        raise _failure(value)
+
+
+def _publish_status(device):
+    """Stream-ordered 4-byte copy of the sticky word to pinned host memory (capturable in a CUDA graph)."""
+    words, mirror = _status(device)
+    mirror.copy_(words[1:], non_blocking=True)
+
+
+def check_status(device):
+    """Synchronise and raise if any attention launch on ``device`` gave up on a barrier wait since the last check."""
+    words, mirror = _status(device)
+    value = int(words[1].item())
+    if value != 0:
+        words[1:].zero_()
+        mirror.zero_()
+        raise _failure(value)
 
 
 def _validate_packed_view(v):
@@ -80,11 +114,17 @@ def flash_attn_fwd(
 
     q [Sq,H,128] or [B,Sq,H,128] e4m3; k the same with Sk; v like k, or (v_prepacked) the logical
     [Sk,H,128] view of a [H,128,Sk_pad] buffer.  q_descale [B,H,>=ceil(Sq/128)], k_descale
-    [B,H,ceil(Sk/128)], v_descale [B,H], all float32.  cu_seqlens_* / max_seqlen_* are accepted for
-    signature compatibility; a 3-D call is one sequence spanning the whole tensor.
+    [B,H,ceil(Sk/128)], v_descale [B,H], all float32.  A 3-D call is one sequence spanning the whole tensor:
+    cu_seqlens_* may be passed only in the single-sequence form the reference's public functions build
+    (int32 [2] = [0, S], api.py:52-55; its values are the caller's contract and are not read), max_seqlen_*
+    only equal to the tensor's length; packed multi-sequence input raises instead of attending across
+    sequences.
     v_smooth: V holds residual codes of one sequence, ``v_smooth_means`` [1,ceil(Sk/128),H,128] (float32 or
     bfloat16) the block means in code units and ``v_smooth_scale`` [1,H,128] float32 the channel scales; no
     descales are taken on that path.
+
+    A launch whose bounded waits expire leaves NaN in its output; that is reported by the next call on the
+    device (without synchronising) or by ``check_status`` (which synchronises).
     """
     if unsupported:
         raise NotImplementedError(f"Unsupported kernel options in this build: {sorted(unsupported)}")
@@ -94,6 +134,17 @@ def flash_attn_fwd(
         raise ValueError("causal attention uses the plain key scan (mid_window_blocks=None) and takes no repair prefix or V-Smooth")
     if any(t.dtype != torch.float8_e4m3fn for t in (q, k, v)):
         raise ValueError("ExpCast attention expects float8_e4m3fn Q/K/V")
+    for name, cu, t, given_max in (("q", cu_seqlens_q, q, max_seqlen_q), ("k", cu_seqlens_k, k, max_seqlen_k)):
+        if cu is not None:
+            if t.ndim != 3:
+                raise ValueError(f"cu_seqlens_{name} goes with packed [S,H,128] input, not with a batched tensor")
+            if tuple(cu.shape) != (2,):
+                raise NotImplementedError(
+                    f"cu_seqlens_{name} with {cu.numel() - 1} sequences: packed multi-sequence (varlen) input is not "
+                    "built; call once per sequence"
+                )
+        if given_max is not None and t.ndim >= 3 and int(given_max) != t.shape[-3]:
+            raise ValueError(f"max_seqlen_{name}={given_max} does not match the sequence length {t.shape[-3]}")
     if v_smooth:
         return _v_smooth_forward(q, k, v, v_smooth_means, v_smooth_scale, softmax_scale, mid_window_blocks,
                                  (q_descale, k_descale, v_descale, repair_k_descale), v_prepacked), None
@@ -157,6 +208,7 @@ def flash_attn_fwd(
         raise ValueError("mid_window_blocks must be None or >= 0")
 
     lib = _lib.load()
+    _raise_if_flagged(device)
     with torch.cuda.device(device):
         if v_prepacked:
             packed_ptr = v.data_ptr()
@@ -190,6 +242,7 @@ def flash_attn_fwd(
                 ),
                 "ovc_attention",
             )
+        _publish_status(device)
         del keep
     return out, lse
 
@@ -242,6 +295,7 @@ def _v_smooth_forward(q, k, v, means, scale, softmax_scale, mid_window_blocks, d
     if window < -1:
         raise ValueError("mid_window_blocks must be None or >= 0")
     lib = _lib.load()
+    _raise_if_flagged(device)
     with torch.cuda.device(device):
         from .quantization import pack_v
 
@@ -259,6 +313,7 @@ def _v_smooth_forward(q, k, v, means, scale, softmax_scale, mid_window_blocks, d
             ),
             "ovc_attention_vsmooth",
         )
+        _publish_status(device)
         del packed
     return out
 

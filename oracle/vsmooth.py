@@ -10,12 +10,15 @@ Parity status: unpinned.  The reference's grouping uses BF16 tensor-core product
 order is not specified, so labels of near-tied tokens (and with them the permutation) can differ between
 implementations; tests therefore replay a given permutation and compare everything downstream of it.
 Block sums are taken in float32 in the fixed two-level order of the CUDA kernel (see block_sum); the
-reference's Triton reduction order is unspecified.
+reference's Triton reduction order is unspecified (on a B200 its means differ from these by at most a few ulp,
+tests/test_gpu_prep_hw.py).  Everything computed from given block means is pinned bit for bit by the fixture the
+reference's kernels produced on a B200 (tests/golden/prep_golden_gpu.npz, test_oracle_golden.py).
 """
 
 import numpy as np
 
 from .fp8 import e4m3_encode
+from .prep import GPU
 
 F32 = np.float32
 BLOCK = 128
@@ -73,16 +76,20 @@ def block_sum(rows):
     return total
 
 
-def apply_v_smooth(q, k, v, permutation):
+def apply_v_smooth(q, k, v, permutation, arith=GPU, block_means=None):
     """Permute K/V by group, demean V per 128-token block, quantise.  q,k,v float32 [S,H,128] (BF16 values),
     permutation int [H,S].  Returns dict(q, k, v codes uint8 [S,H,128], means f32 [blocks,H,128] (BF16-rounded,
-    in code units), scale f32 [H,128])."""
+    in code units), scale f32 [H,128], block_means f32 [H,blocks,128], amax f32 [H,128]).  ``arith`` evaluates the
+    divisions as the reference's GPU code does (oracle/prep.py); ``block_means`` (f32 [H,blocks,128]) replaces the
+    block means computed here, whose float32 summation order the reference leaves to its compiler."""
     s, h, d = v.shape
     blocks = (s + BLOCK - 1) // BLOCK
     k8 = np.zeros((s, h, d), dtype=np.uint8)
     v8 = np.zeros((s, h, d), dtype=np.uint8)
     means_out = np.zeros((blocks, h, d), dtype=F32)
     scale_out = np.zeros((h, d), dtype=F32)
+    all_means = np.zeros((h, blocks, d), dtype=F32)
+    all_amax = np.zeros((h, d), dtype=F32)
     for head in range(h):
         vp = v[permutation[head], head]  # [S,128] in group order
         kp = k[permutation[head], head]
@@ -90,15 +97,22 @@ def apply_v_smooth(q, k, v, permutation):
         amax = np.zeros(d, dtype=F32)
         for b in range(blocks):
             rows = vp[b * BLOCK : (b + 1) * BLOCK]
-            means[b] = (block_sum(rows) / F32(rows.shape[0])).astype(F32)
+            if block_means is not None:
+                means[b] = block_means[head, b]
+            else:
+                total = block_sum(rows)
+                means[b] = arith.div(total, np.full_like(total, F32(rows.shape[0])))
             amax = np.maximum(amax, np.abs((rows - means[b][None, :]).astype(F32)).max(axis=0))
-        scale = np.where(amax > 0, (amax / F32(448.0)).astype(F32), F32(1.0)).astype(F32)
+        positive = np.where(amax > 0, amax, F32(448.0)).astype(F32)
+        scale = np.where(amax > 0, arith.div(positive, np.full_like(positive, F32(448.0))), F32(1.0)).astype(F32)
+        all_means[head], all_amax[head] = means, amax
         for b in range(blocks):
             rows = vp[b * BLOCK : (b + 1) * BLOCK]
-            codes = np.clip(((rows - means[b][None, :]).astype(F32) / scale[None, :]).astype(F32), -448.0, 448.0)
+            residual = (rows - means[b][None, :]).astype(F32)
+            codes = np.clip(arith.div(residual, np.broadcast_to(scale[None, :], residual.shape)), -448.0, 448.0)
             v8[b * BLOCK : b * BLOCK + rows.shape[0], head] = e4m3_encode(codes)
-            means_out[b, head] = _bf16((means[b] / scale).astype(F32))
+            means_out[b, head] = _bf16(arith.div(means[b], scale))
         k8[:, head] = e4m3_encode(np.clip(kp, -448.0, 448.0))
         scale_out[head] = scale
     q8 = e4m3_encode(np.clip(q, -448.0, 448.0))
-    return dict(q=q8, k=k8, v=v8, means=means_out, scale=scale_out)
+    return dict(q=q8, k=k8, v=v8, means=means_out, scale=scale_out, block_means=all_means, amax=all_amax)

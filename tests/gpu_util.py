@@ -59,7 +59,7 @@ def hw_div(a, b):
     lib = _lib.load()
     a = np.ascontiguousarray(a, dtype=np.float32)
     b = np.ascontiguousarray(np.broadcast_to(np.asarray(b, dtype=np.float32), a.shape))
-    ta, tb = torch.from_numpy(a.reshape(-1)).to(DEV), torch.from_numpy(b.reshape(-1)).to(DEV)
+    ta, tb = torch.from_numpy(a.reshape(-1).copy()).to(DEV), torch.from_numpy(b.reshape(-1).copy()).to(DEV)
     tq = torch.empty_like(ta)
     _lib.check(lib.ovc_div_full(ta.data_ptr(), tb.data_ptr(), tq.data_ptr(), ta.numel(), _lib.stream_pointer(DEV)), "ovc_div_full")
     return tq.cpu().numpy().reshape(a.shape)

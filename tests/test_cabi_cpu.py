@@ -81,5 +81,14 @@ def test_null_and_bad_arguments_are_rejected_without_a_gpu(lib):
     assert lib.ovc_vs_update_centers(null, p, p, 1, 8, null) == bad
     assert lib.ovc_vs_block_stats(p, null, p, p, 128, 1, null) == bad
     assert lib.ovc_vs_block_write(p, p, p, p, p, p, null, p, p, 128, 1, null) == bad
+    assert lib.ovc_vs_block_stats(p + 2, p, p, p, 128, 1, null) == bad           # misaligned V
+    assert lib.ovc_vs_block_stats(p, p + 4, p, p, 128, 1, null) == bad           # misaligned permutation
+    assert lib.ovc_vs_block_write(p, p + 8, p, p, p, p, p, p, p, 128, 1, null) == bad   # misaligned V
+    assert lib.ovc_vs_block_write(p, p, p, p, p, p + 4, p, p, p, 128, 1, null) == bad   # misaligned K codes
+    assert lib.ovc_vs_block_write(p, p, p, p, p, p, p + 2, p, p, 128, 1, null) == bad   # misaligned V codes
+    assert lib.ovc_div_full(null, p, p, 4, null) == bad
+    assert lib.ovc_div_full(p, p, p, 0, null) == bad
+    assert lib.ovc_selftest_wait(null, 1000, p, null) == bad
+    assert lib.ovc_selftest_wait(p, 0, p, null) == bad
     assert lib.ovc_cast_e4m3(p, 1, p, 12, null) == bad                     # not a multiple of 8
     assert lib.ovc_cast_e4m3(p, 9, p, 16, null) == bad                     # dtype

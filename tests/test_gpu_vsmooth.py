@@ -12,7 +12,7 @@ from oracle import vsmooth as ovs
 
 pytestmark = pytest.mark.gpu
 
-from gpu_util import DEV, f32, structured_qkv, u8  # noqa: E402
+from gpu_util import DEV, f32, hw_arith, structured_qkv, u8  # noqa: E402
 
 ORACLE_TOL = 5e-3
 
@@ -58,7 +58,7 @@ def test_preparation_is_bit_exact_for_a_replayed_grouping(s, h, clusters):
     prepared = baselines.prepare_vc(q, k, v, clusters=clusters, iterations=3)
     perm = prepared.permutation.cpu().numpy().reshape(h, s)
     assert all(np.array_equal(np.sort(perm[i]), np.arange(s)) for i in range(h))
-    want = ovs.apply_v_smooth(f32(q), f32(k), f32(v), perm)
+    want = ovs.apply_v_smooth(f32(q), f32(k), f32(v), perm, arith=hw_arith())
     assert np.array_equal(u8(prepared.q), want["q"])
     assert np.array_equal(u8(prepared.k), want["k"])
     assert np.array_equal(u8(prepared.v), want["v"])

@@ -269,3 +269,26 @@ def test_benchmark_command_line_rules(capsys):
         import re
 
         assert re.search(message, capsys.readouterr().err)
+
+
+def test_kernel_interface_rejects_packed_multi_sequence_metadata():
+    """cu_seqlens with more than one sequence, metadata on batched input and a wrong max_seqlen raise before
+    anything touches a GPU (the reference's kernel would treat the first as varlen input)."""
+    import torch
+
+    from open_vc_attn import forward
+
+    q = torch.zeros(256, 2, 128).to(torch.float8_e4m3fn)
+    args = dict(q_descale=torch.ones(1, 2, 2), k_descale=torch.ones(1, 2, 2), v_descale=torch.ones(1, 2), expcast=True)
+    three = torch.tensor([0, 100, 256], dtype=torch.int32)
+    with pytest.raises(NotImplementedError, match="varlen"):
+        forward.flash_attn_fwd(q, q, q, cu_seqlens_q=three, **args)
+    with pytest.raises(NotImplementedError, match="varlen"):
+        forward.flash_attn_fwd(q, q, q, cu_seqlens_k=three, **args)
+    with pytest.raises(ValueError, match="max_seqlen_q"):
+        forward.flash_attn_fwd(q, q, q, max_seqlen_q=100, **args)
+    with pytest.raises(ValueError, match="max_seqlen_k"):
+        forward.flash_attn_fwd(q, q, q, max_seqlen_k=255, **args)
+    q4 = q[None]
+    with pytest.raises(ValueError, match="batched"):
+        forward.flash_attn_fwd(q4, q4, q4, cu_seqlens_q=torch.tensor([0, 256], dtype=torch.int32), **args)

@@ -154,6 +154,24 @@ def test_repair_pieces_match_the_reference_on_hardware(golden, hw):
     assert np.allclose(out["score"], hw["hw_repair_score"], rtol=2e-6, atol=0)
 
 
+def test_v_smooth_block_kernels_match_the_reference_on_hardware(hw):
+    """Downstream of the reference's own block means (a Triton reduction), codes, scales and scaled means are
+    reproduced bit for bit; the oracle's own means are within a few ulp of the reference's."""
+    from oracle import vsmooth
+
+    k, v = bf16(hw["vs_k_bf16"]), bf16(hw["vs_v_bf16"])
+    arith = hw_arith(hw)
+    out = vsmooth.apply_v_smooth(np.zeros_like(k), k, v, hw["vs_perm"], arith=arith, block_means=hw["vs_block_means"])
+    assert np.array_equal(out["amax"], hw["vs_amax"])
+    assert np.array_equal(out["scale"], hw["vs_scale"][0])
+    assert np.array_equal(out["k"], hw["vs_k_out"])
+    assert np.array_equal(out["v"], hw["vs_codes"])
+    assert np.array_equal(out["means"], hw["vs_means_out"][0])
+    own = vsmooth.apply_v_smooth(np.zeros_like(k), k, v, hw["vs_perm"], arith=arith)
+    ulp = np.abs(own["block_means"].view(np.int32).astype(np.int64) - hw["vs_block_means"].view(np.int32).astype(np.int64))
+    assert ulp.max() <= 4
+
+
 def test_repair_counts_follow_the_reference_examples():
     # docs/api.md:72 and tests/gpu/test_repair_cli.py:69-70 of the reference
     assert prep.repair_counts(0.005, 73397) == (367, 384)
