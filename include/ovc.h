@@ -178,6 +178,15 @@ int ovc_attention(const void* q8, const void* k8, const void* v_packed, const fl
                   float softmax_scale, int mid_window_blocks, uint32_t* status, void* stream);
 
 /*
+ * Measurement aid: runs the attention kernel's score conversion alone (tcgen05.ld of 128 scores, row max,
+ * ExpCast codes, tcgen05.st) in `ctas` CTAs of 8 conversion warps, `tiles` key tiles each, on scores held in
+ * tensor memory.  Timed by the caller, ctas * 256 * 128 * tiles scores per launch give the rate the CUDA cores
+ * sustain without exp instructions: the denominator of the MUFU-free ExpCast roofline.  `sink`: one uint32 in
+ * device memory (never written in practice).  No counterpart in the reference.
+ */
+int ovc_bench_conversion(uint32_t* sink, int64_t ctas, int64_t tiles, void* stream);
+
+/*
  * Runs the kernels' bounded barrier wait on its own: one 64-thread CTA waits at most `limit_cycles` clock
  * ticks on a barrier that cannot complete, then sets OVC_STATUS_WAIT_EXPIRED in status[0] and status[1] (the
  * two words ovc_attention takes) and adds the number of threads that gave up to *gave_up (device memory).  No tensor-core work or copy is in flight, the

@@ -29,6 +29,7 @@ SIGNATURES = {
     "ovc_repair_score": (_i, [_p, _i, _l, _l, _p, _p, _p, _p]),
     "ovc_repair_rows": (_i, [_p, _p, _p, _i, _p, _p, _p, _p, _l, _l, _l, _l, _l, _p]),
     "ovc_attention": (_i, [_p, _p, _p, _p, _l, _p, _p, _p, _l, _p, _l, _l, _l, _l, _f, _i, _p, _p]),
+    "ovc_bench_conversion": (_i, [_p, _l, _l, _p]),
     "ovc_selftest_wait": (_i, [_p, _l, _p, _p]),
     "ovc_copy_head_slice": (_i, [_p, _l, _l, _p, _l, _l, _l, _l, _l, _i, _p]),
     "ovc_attention_ex": (_i, [_p, _p, _p, _p, _l, _p, _p, _p, _l, _p, _p, _i, _l, _l, _l, _l, _f, _i, _p, _p]),

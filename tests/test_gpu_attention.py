@@ -196,26 +196,22 @@ def test_prepacked_contract_errors():
         api.attention_fp8(broken)
 
 
-def test_diffusion_adapter_packed_sequences_and_padding(monkeypatch):
-    # tests/gpu/test_attention.py:69-87 of the reference
-    from open_vc_attn.integrations.diffusion import DenseDiffusionAdapter
-
-    monkeypatch.setenv("OPEN_VC_ATTN_IMPLEMENTATION", "open-vc")
-    monkeypatch.setenv("OPEN_VC_ATTN_MODE", "expcast")
-    impl = DenseDiffusionAdapter(2, 128, 128**-0.5)
+def test_packed_sequences_are_attended_one_call_per_sequence():
+    """What the reference's diffusion adapter relies on (tests/gpu/test_attention.py:69-87 of the reference):
+    a caller that splits a packed [T,H,128] tensor at its sequence bounds gets, per sequence, exactly the
+    result of that sequence alone - no scale block and no V scale crosses a bound, whatever lies beside it."""
+    ovc, api, forward = _api()
     torch.manual_seed(513)
     q, k, v = [torch.randn(258, 2, 128, device=DEV, dtype=torch.bfloat16) for _ in range(3)]
     bounds = (0, 129, 258)
-    cu = torch.tensor(bounds, device=DEV, dtype=torch.int32)
-    out = impl.forward_varlen(q, k, v, cu_seqlens=cu, max_seqlen=129, cu_seqlens_host=bounds)
-    for a, b in zip(bounds, bounds[1:]):
-        assert torch.equal(out[a:b], impl.forward(q[a:b], k[a:b], v[a:b]))
-    padded = DenseDiffusionAdapter(2, 128, 128**-0.5, packed_trailing_padding=True)
-    out = padded.forward_varlen(q, k, v, cu_seqlens=cu, max_seqlen=129, cu_seqlens_host=bounds)
-    assert torch.count_nonzero(out[129:]) == 0
-    assert torch.equal(out[:129], impl.forward(q[:129], k[:129], v[:129]))
-    with pytest.raises(ValueError):
-        impl.forward_varlen(q, k, v, cu_seqlens=cu, max_seqlen=129)
+    alone = [ovc.attention(q[a:b].clone(), k[a:b].clone(), v[a:b].clone(), softmax_scale=128**-0.5)
+             for a, b in zip(bounds, bounds[1:])]
+    views = [ovc.attention(q[a:b], k[a:b], v[a:b], softmax_scale=128**-0.5) for a, b in zip(bounds, bounds[1:])]
+    forward.check_status(q.device)
+    for one, other in zip(alone, views):
+        assert torch.equal(one, other)
+    whole = ovc.attention(q, k, v, softmax_scale=128**-0.5)
+    assert not torch.equal(whole[:129], alone[0])  # attending across the bound is a different result
 
 
 @pytest.mark.parametrize("shape", [(300, 2), (2, 700, 3)])
