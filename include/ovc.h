@@ -276,10 +276,17 @@ int ovc_cast_e4m3(const void* x, int dtype, void* out, int64_t elements, void* s
  *   v_packed      [H,128,Sk_pad] fp8 residual codes (ovc_pack_v of the codes)
  *   unit_descale  f32, at least H * ceil(max(Sq,Sk)/128) values, all 1.0
  *   means         [ceil(Sk/128),H,128] f32; channel_scale [H,128] f32
+ *   workspace     device scratch of ovc_attention_vsmooth_workspace(Sk, H) bytes, 16-byte aligned; the call
+ *                 fills it (the means as BF16 high and low parts in the layout its tensor-core products read)
+ *                 and it may be reused or freed once the stream has passed the call
+ * The restoration runs on the tensor core as in the reference (cute/flash_fwd_sm100.py:4482-4526): the masses
+ * of sixteen key blocks at a time times their means, masses and means each split into two BF16 terms.
  */
+int64_t ovc_attention_vsmooth_workspace(int64_t Sk, int64_t H);
 int ovc_attention_vsmooth(const void* q8, const void* k8, const void* v_packed, const float* unit_descale,
-                          const float* means, const float* channel_scale, void* out, int64_t Sq, int64_t Sk,
-                          int64_t H, float softmax_scale, int mid_window_blocks, uint32_t* status, void* stream);
+                          const float* means, const float* channel_scale, void* workspace, void* out, int64_t Sq,
+                          int64_t Sk, int64_t H, float softmax_scale, int mid_window_blocks, uint32_t* status,
+                          void* stream);
 
 #ifdef __cplusplus
 }

@@ -25,7 +25,8 @@
 //
 // Tensor memory map (512 columns): S 0..127 (shared by both stages), P0 128..159, P1 160..191,
 // O0 192..327, O1 328..463; each O region is 128 output columns followed by 8 copies of the
-// denominator (the PV product has N = 136).
+// denominator (the PV product has N = 136).  The V-Smooth variant also uses W0 464..479 and W1 480..495:
+// per stage the probability masses of sixteen key blocks as BF16 high parts (8 columns) and low parts (8).
 
 #include <atomic>
 
@@ -48,7 +49,9 @@ constexpr int kTileBytes = kTile * kDim;          // 16384: one FP8 tile, 128 ro
 constexpr int kOnesRows = 8;                      // extension of the PV product that sums P
 constexpr int kVSlotBytes = kTileBytes + kOnesRows * 128;
 constexpr int kPvN = kDim + kOnesRows;            // 136
-constexpr uint32_t kColS = 0, kColP = 128, kColO = 192, kColOStride = kPvN, kTmemCols = 512;
+constexpr uint32_t kColS = 0, kColP = 128, kColO = 192, kColOStride = kPvN, kColW = 464, kTmemCols = 512;
+constexpr int kMeanGroup = 32;                    // key blocks per tile of block means (V-Smooth)
+constexpr int kMeanSlice = 16;                    // key blocks restored by one group of BF16 products
 constexpr long long kWaitCycles = 400000000LL;    // bounded barrier wait (~0.2 s)
 constexpr uint32_t kSleepHintNs = 100000;         // one hardware-suspended try_wait lasts at most this
 
@@ -64,8 +67,12 @@ struct SmemLayout {
     uint64_t p_full[2];   // the stage has stored its probabilities of the step (+ V tile landed for p_full[0])
     uint64_t pv_done[2];  // the stage's previous PV has been accumulated (commit)
     uint64_t o_full[2], drain[2];
+    uint64_t m_full[2], m_free[2];  // V-Smooth: a tile of block means has landed / its last reader is done (commit)
     uint32_t tmem_base;
     volatile uint32_t abort_flag;
+    // V-Smooth only (the other variants do not allocate it): two tiles of block means, 128 channels x 128 bytes
+    // = BF16 high parts of 32 key blocks, then their low parts, in the 128-byte swizzle.
+    alignas(1024) uint8_t means[2][kTileBytes];
 };
 
 struct AttnParams {
@@ -263,7 +270,8 @@ __device__ __forceinline__ void poison_row(const AttnParams& p, int batch, int h
 template <bool kVS, bool kCausal>
 __global__ void __launch_bounds__(kThreads, 1)
 attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
-                 const __grid_constant__ CUtensorMap tmap_v, const AttnParams p) {
+                 const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_m,
+                 const AttnParams p) {
     extern __shared__ uint8_t smem_raw[];
     SmemLayout& sm = *reinterpret_cast<SmemLayout*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
 
@@ -316,6 +324,10 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         mbar_init(smem_addr(&sm.p_full[1]), 128);
         mbar_init(smem_addr(&sm.drain[0]), 1);
         mbar_init(smem_addr(&sm.drain[1]), 1);
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(smem_addr(&sm.m_full[i]), 1);
+            mbar_init(smem_addr(&sm.m_free[i]), 1);
+        }
         sm.abort_flag = 0;
         mbar_init_fence();
     }
@@ -348,10 +360,20 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
                     tma_load_4d(smem_addr(sm.q[s]), &tmap_q, smem_addr(&sm.q_full[s]), 0, head,
                                 (2 * m_block + s) * kTile, batch, stream);
                 }
-                int issued_k = 0, issued_v = 0;
+                int issued_k = 0, issued_v = 0, issued_m = 0, j_before = 0;
                 for (int it = 0; it < n_iters; ++it) {
                     const int j = tile_at(it, j0, p.first_tile, n_tiles);
                     const int ks = it % kKStages, vs = it % kVStages;
+                    if (kVS && (it == 0 || j / kMeanGroup != j_before / kMeanGroup)) {
+                        // The scan enters another group of 32 key blocks: fetch its means.  The buffer's previous
+                        // group was left two groups ago; the PV issuer commits m_free when it leaves a group.
+                        const int b = issued_m & 1;
+                        if (issued_m >= 2 && !wait_bar(sm, &sm.m_free[b], ((issued_m >> 1) - 1) & 1, p.status)) break;
+                        mbar_expect_tx(smem_addr(&sm.m_full[b]), kTileBytes);
+                        tma_load_4d(smem_addr(sm.means[b]), &tmap_m, smem_addr(&sm.m_full[b]), (j / kMeanGroup) * 128, 0, head, 0, keep);
+                        ++issued_m;
+                    }
+                    j_before = j;
                     // K(it - kKStages) was last read by stage 1's QK of that step; stage 1 releases the slot
                     // when it sees those scores.
                     if (it >= kKStages &&
@@ -368,6 +390,14 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
                     mbar_expect_tx(smem_addr(&sm.v_full[vs]), kTileBytes);
                     tma_load_4d(smem_addr(sm.v[vs]), &tmap_v, smem_addr(&sm.v_full[vs]), j * kTile, 0, head, batch, keep);
                     issued_v = it + 1;
+                }
+                if (kVS) {
+                    // A group whose blocks never complete a slice has no reader: its copy must still have landed
+                    // before the CTA exits.
+                    for (int c = max(0, issued_m - 2); c < issued_m; ++c) {
+                        const long long t0 = clock64();
+                        while (!mbar_try_wait(smem_addr(&sm.m_full[c & 1]), (c >> 1) & 1) && clock64() - t0 < kWaitCycles) {}
+                    }
                 }
                 if (sm.abort_flag) {
                     // Give the copies already issued a bounded time to land before the CTA exits.
@@ -421,16 +451,40 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
             // ---------------- PV issuer ----------------
             // p_full[s] completion n: stage s has stored P_s(n) and V(n) has landed.
             constexpr uint32_t idesc_pv = idesc_e4m3_f32(kPvN);
+            constexpr uint32_t idesc_mean = idesc_bf16_f32(kDim);
             bool ok = true;
+            int groups_left = 0;  // V-Smooth: groups of block means the scan has left (buffer groups_left & 1 is current)
             for (int n = 0; ok && n < n_iters; ++n) {
+                // V-Smooth: when the previous step closed a slice of sixteen key blocks, the stages have stored the
+                // slice's masses with this step's probabilities; O += W_hi M_hi + W_lo M_hi + W_hi M_lo goes first.
+                bool restore = false, leave_group = false;
+                uint32_t mean_lo = 0;
+                if (kVS && n > 0) {
+                    const int j_done = tile_at(n - 1, j0, p.first_tile, n_tiles);
+                    restore = (j_done % kMeanSlice) == 0;
+                    leave_group = tile_at(n, j0, p.first_tile, n_tiles) / kMeanGroup != j_done / kMeanGroup;
+                    if (restore) {
+                        ok = __all_sync(0xFFFFFFFFu, wait_bar(sm, &sm.m_full[groups_left & 1], (groups_left >> 1) & 1, p.status));
+                        if (!ok) break;
+                        mean_lo = smem_desc_lo(smem_addr(sm.means[groups_left & 1])) + 2 * ((j_done % kMeanGroup) / kMeanSlice);
+                    }
+                }
                 for (int s = 0; s < 2; ++s) {
                     ok = __all_sync(0xFFFFFFFFu, wait_bar(sm, &sm.p_full[s], n & 1, p.status));
                     if (!ok) break;
                     tc_fence_after();
+                    if (kVS && restore) {
+                        const uint32_t w_hi = tmem + kColW + 16 * s, w_lo = w_hi + 8;
+                        mma_bf16_ts(tmem + kColO + s * kColOStride, w_hi, mean_lo, idesc_mean);
+                        mma_bf16_ts(tmem + kColO + s * kColOStride, w_lo, mean_lo, idesc_mean);
+                        mma_bf16_ts(tmem + kColO + s * kColOStride, w_hi, mean_lo + 4, idesc_mean);
+                    }
                     mma4_f8_ts(tmem + kColO + s * kColOStride, tmem + kColP + 32 * s,
                                smem_desc_lo(smem_addr(sm.v[n % kVStages])), idesc_pv, n > 0 ? 1u : 0u);
+                    if (kVS && leave_group && s == 1) mma_commit_elect(smem_addr(&sm.m_free[groups_left & 1]));
                     mma_commit_elect(smem_addr(n + 1 < n_iters ? &sm.pv_done[s] : &sm.o_full[s]));
                 }
+                if (leave_group) ++groups_left;
             }
             if (!ok) drain_mmas(sm, 1);
         } else if (warp == 10) {
@@ -470,6 +524,12 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         float row_max = 0.0f, bias = 0.0f, saved_denominator = 0.0f;
         float l_known = 0.0f;  // V-Smooth: denominator before the previous step's PV, after rescaling
         int j_prev = 0;        // V-Smooth: key tile of the previous step
+        // V-Smooth: probability masses of the key blocks of the current slice (slot = block % 16) whose means
+        // have not been added to the accumulator yet, in the accumulator's current scale.
+        float mass[kVS ? kMeanSlice : 1];
+#pragma unroll
+        for (int i = 0; i < (kVS ? kMeanSlice : 1); ++i) mass[i] = 0.0f;
+        const uint32_t t_w = lane_base + kColW + 16 * stage;
         bool ok = true;
         for (int it = 0; it < n_iters; ++it) {
             const int j = tile_at(it, j0, p.first_tile, n_tiles);
@@ -544,37 +604,48 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
             }
             tmem_st32(t_p, codes);
 
+            const bool rescale = it > 0 && __any_sync(0xFFFFFFFFu, alpha < 1.0f);
             if (kVS) {
                 if (it > 0) {
-                    // The previous PV has landed: its tile's probability sum is the growth of the denominator.
-                    // Add that sum times the tile's block mean to the accumulator, then apply this step's rescale.
+                    // The previous PV has landed: its tile's probability sum is the growth of the denominator.  The
+                    // sum joins the pending masses; every pending mass follows the accumulator's rescaling.
                     const float l_cur = __uint_as_float(tmem_ld1(t_o + kDim));
                     tmem_wait_ld();
                     const float w = l_cur - l_known;
-                    const float4* mean4 = reinterpret_cast<const float4*>(
-                        p.vs_means + (static_cast<long long>(j_prev) * p.H + head) * kDim);
+                    const int slot = j_prev % kMeanSlice;
 #pragma unroll
-                    for (int c = 0; c < 4; ++c) {
-                        uint32_t o[32];
-                        tmem_ld32(t_o + 32 * c, o);
-                        tmem_wait_ld();
-#pragma unroll
-                        for (int e = 0; e < 8; ++e) {
-                            const float4 m = __ldg(mean4 + 8 * c + e);
-                            o[4 * e] = __float_as_uint(fmaf(w, m.x, __uint_as_float(o[4 * e])) * alpha);
-                            o[4 * e + 1] = __float_as_uint(fmaf(w, m.y, __uint_as_float(o[4 * e + 1])) * alpha);
-                            o[4 * e + 2] = __float_as_uint(fmaf(w, m.z, __uint_as_float(o[4 * e + 2])) * alpha);
-                            o[4 * e + 3] = __float_as_uint(fmaf(w, m.w, __uint_as_float(o[4 * e + 3])) * alpha);
-                        }
-                        tmem_st32(t_o + 32 * c, o);
-                    }
+                    for (int i = 0; i < kMeanSlice; ++i) mass[i] = (i == slot ? w : mass[i]) * alpha;
                     l_known = l_cur * alpha;
-                    tmem_st1(t_o + kDim, __float_as_uint(l_known));
+                    if (rescale) {
+#pragma unroll
+                        for (int c = 0; c < 4; ++c) {
+                            uint32_t o[32];
+                            tmem_ld32(t_o + 32 * c, o);
+                            tmem_wait_ld();
+#pragma unroll
+                            for (int e = 0; e < 32; ++e) o[e] = __float_as_uint(__uint_as_float(o[e]) * alpha);
+                            tmem_st32(t_o + 32 * c, o);
+                        }
+                        tmem_st1(t_o + kDim, __float_as_uint(l_known));
+                    }
+                    if (slot == 0) {
+                        // The slice is complete: hand its masses to the tensor core as BF16 high and low parts
+                        // (the PV issuer adds masses x block means to the accumulator before this step's PV).
+                        uint32_t hi[8], lo[8];
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) {
+                            hi[i] = bf16x2(mass[2 * i], mass[2 * i + 1]);
+                            lo[i] = bf16x2(mass[2 * i] - __uint_as_float(hi[i] << 16),
+                                           mass[2 * i + 1] - __uint_as_float(hi[i] & 0xFFFF0000u));
+                            mass[2 * i] = 0.0f, mass[2 * i + 1] = 0.0f;
+                        }
+                        tmem_st8(t_w, hi);
+                        tmem_st8(t_w + 8, lo);
+                    }
                 }
                 j_prev = j;
             } else {
                 const bool first_repair = p.first_tile > 0 && j == p.first_tile - 1;
-                const bool rescale = it > 0 && __any_sync(0xFFFFFFFFu, alpha < 1.0f);
                 if (first_repair) {
                     // First repair tile: the denominator holds the original tokens' total only.
                     saved_denominator = __uint_as_float(tmem_ld1(t_o + kDim));
@@ -605,7 +676,12 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
             tc_fence_after();
             float l = __uint_as_float(tmem_ld1(t_o + kDim));
             tmem_wait_ld();
-            const float w_last = l - l_known;  // V-Smooth: probability sum of the last tile
+            if (kVS) {
+                const float w_last = l - l_known;  // probability sum of the last tile
+#pragma unroll
+                for (int i = 0; i < kMeanSlice; ++i)
+                    if (i == j_prev % kMeanSlice) mass[i] = w_last;
+            }
             if (p.first_tile > 0) l = saved_denominator;
             const bool bad = l == 0.0f || l != l;
             float inv;
@@ -618,7 +694,10 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
                 p.lse[bh_l * p.Sq + static_cast<long long>(q_tile) * kTile + row_in_tile] =
                     bad ? -INFINITY : (fmaf(row_max, sigma, lg) - 8.0f) * 0.6931471805599453f;
             }
-            const float* mean_last = kVS ? p.vs_means + (static_cast<long long>(j_prev) * p.H + head) * kDim : nullptr;
+            // V-Smooth: the masses still pending belong to the slice of the last tile visited; their means are
+            // added here on the CUDA cores (once per CTA).
+            const int slice_first = j_prev / kMeanSlice * kMeanSlice;
+            const float* slice_means = kVS ? p.vs_means + (static_cast<long long>(slice_first) * p.H + head) * kDim : nullptr;
             const float* channel_scale = kVS ? p.vs_scale + static_cast<long long>(head) * kDim : nullptr;
             const long long row = static_cast<long long>(q_tile) * kTile + row_in_tile;
             uint4* dst = reinterpret_cast<uint4*>(p.out + ((static_cast<long long>(batch) * p.Sq + row) * p.H + head) * kDim);
@@ -629,9 +708,23 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
                 tmem_wait_ld();
                 if (kVS) {
 #pragma unroll
+                    for (int i = 0; i < kMeanSlice; ++i) {
+                        if (slice_first + i < p.n_tiles) {
+                            const float4* mean4 = reinterpret_cast<const float4*>(
+                                slice_means + static_cast<long long>(i) * p.H * kDim + 32 * c);
+#pragma unroll
+                            for (int e = 0; e < 8; ++e) {
+                                const float4 m = __ldg(mean4 + e);
+                                o[4 * e] = __float_as_uint(fmaf(mass[i], m.x, __uint_as_float(o[4 * e])));
+                                o[4 * e + 1] = __float_as_uint(fmaf(mass[i], m.y, __uint_as_float(o[4 * e + 1])));
+                                o[4 * e + 2] = __float_as_uint(fmaf(mass[i], m.z, __uint_as_float(o[4 * e + 2])));
+                                o[4 * e + 3] = __float_as_uint(fmaf(mass[i], m.w, __uint_as_float(o[4 * e + 3])));
+                            }
+                        }
+                    }
+#pragma unroll
                     for (int e = 0; e < 32; ++e)
-                        o[e] = __float_as_uint(fmaf(w_last, __ldg(mean_last + 32 * c + e), __uint_as_float(o[e])) *
-                                               __ldg(channel_scale + 32 * c + e));
+                        o[e] = __float_as_uint(__uint_as_float(o[e]) * __ldg(channel_scale + 32 * c + e));
                 }
                 if (row < p.Sq) {
 #pragma unroll
@@ -654,6 +747,33 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
     if (warp == 9) {
         tc_fence_after();
         tmem_dealloc(tmem, kTmemCols);
+    }
+}
+
+// V-Smooth: block means [n_tiles, H, 128] float32 -> the layout the attention kernel loads by TMA and multiplies as
+// the B operand of a BF16 product: for every head and channel a row of n_groups x 128 bytes, each 128 bytes holding
+// the BF16 high parts of the 32 key blocks of a group and then their BF16 low parts (mean = high + low to 16 bits;
+// blocks past the end are zero).  One CTA per (group, head), one thread per channel.
+__global__ void __launch_bounds__(kDim) means_split_kernel(const float* __restrict__ means, uint4* __restrict__ out,
+                                                           int n_tiles, int H, int n_groups) {
+    const int g = blockIdx.x, head = blockIdx.y, c = threadIdx.x;
+    uint32_t hi[kMeanGroup / 2], lo[kMeanGroup / 2];
+#pragma unroll
+    for (int t = 0; t < kMeanGroup / 2; ++t) {
+        float m[2];
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+            const int j = g * kMeanGroup + 2 * t + e;
+            m[e] = j < n_tiles ? __ldg(means + (static_cast<long long>(j) * H + head) * kDim + c) : 0.0f;
+        }
+        hi[t] = bf16x2(m[0], m[1]);
+        lo[t] = bf16x2(m[0] - __uint_as_float(hi[t] << 16), m[1] - __uint_as_float(hi[t] & 0xFFFF0000u));
+    }
+    uint4* row = out + ((static_cast<long long>(head) * kDim + c) * n_groups + g) * 8;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        row[i] = make_uint4(hi[4 * i], hi[4 * i + 1], hi[4 * i + 2], hi[4 * i + 3]);
+        row[4 + i] = make_uint4(lo[4 * i], lo[4 * i + 1], lo[4 * i + 2], lo[4 * i + 3]);
     }
 }
 
@@ -781,7 +901,7 @@ namespace {
 
 int launch_attention(const void* q8, const void* k8, const void* v_packed, const float* q_descale, int64_t q_blocks,
                      const float* k_descale, const float* v_descale, const float* repair_kd, int64_t repair_rows,
-                     const float* vs_means, const float* vs_scale, void* out, float* lse, int causal, int64_t B,
+                     const float* vs_means, const float* vs_scale, void* vs_workspace, void* out, float* lse, int causal, int64_t B,
                      int64_t Sq, int64_t Sk, int64_t H, float softmax_scale, int mid_window_blocks, uint32_t* status,
                      void* stream) {
     if (causal && (mid_window_blocks != -1 || repair_rows != 0 || vs_means != nullptr)) return OVC_ERR_ARGUMENT;
@@ -789,7 +909,8 @@ int launch_attention(const void* q8, const void* k8, const void* v_packed, const
         H < 1 || Sq > (1LL << 30) || Sk > (1LL << 30) || q_blocks < ceil_div(Sq, kTile) || !(softmax_scale > 0.0f) ||
         !isfinite(softmax_scale) || mid_window_blocks < -1 || repair_rows < 0 || repair_rows % kTile != 0 ||
         (repair_rows > 0 && (repair_kd == nullptr || repair_rows >= Sk || B != 1)) || !aligned16(q8) ||
-        !aligned16(k8) || !aligned16(v_packed) || !aligned16(out) || (repair_kd && !aligned16(repair_kd)))
+        !aligned16(k8) || !aligned16(v_packed) || !aligned16(out) || (repair_kd && !aligned16(repair_kd)) ||
+        (vs_means && (!vs_workspace || !aligned16(vs_workspace) || B != 1)))
         return OVC_ERR_ARGUMENT;
     const int64_t n_tiles = ceil_div(Sk, kTile), Sk_pad = n_tiles * kTile;
     const int64_t m_blocks = ceil_div(Sq, 2 * kTile);
@@ -803,7 +924,7 @@ int launch_attention(const void* q8, const void* k8, const void* v_packed, const
     if (err != cudaSuccess) { set_last_cuda_error(err); return OVC_ERR_CUDA; }
     if (major != 10 || minor != 0) return OVC_ERR_UNSUPPORTED;  // the library holds sm_100a code only
 
-    CUtensorMap map_q, map_k, map_v;
+    CUtensorMap map_q, map_k, map_v, map_m;
     {
         const cuuint64_t dq[4] = {128, static_cast<cuuint64_t>(H), static_cast<cuuint64_t>(Sq), static_cast<cuuint64_t>(B)};
         const cuuint64_t sq[3] = {128, static_cast<cuuint64_t>(H) * 128, static_cast<cuuint64_t>(Sq) * H * 128};
@@ -819,6 +940,15 @@ int launch_attention(const void* q8, const void* k8, const void* v_packed, const
                                   static_cast<cuuint64_t>(Sk_pad) * 128 * H};
         rc = make_map(&map_v, v_packed, dv, sv, 128, 128, 1);
         if (rc != OVC_OK) return rc;
+        map_m = map_q;  // not read unless V-Smooth
+        if (vs_means != nullptr) {
+            // Rows of n_groups x 128 bytes per (head, channel): see means_split_kernel.
+            const cuuint64_t row_bytes = static_cast<cuuint64_t>(ceil_div(n_tiles, kMeanGroup)) * 128;
+            const cuuint64_t dm[4] = {row_bytes, 128, static_cast<cuuint64_t>(H), 1};
+            const cuuint64_t sm_[3] = {row_bytes, row_bytes * 128, row_bytes * 128 * H};
+            rc = make_map(&map_m, vs_workspace, dm, sm_, 128, 128, 1);
+            if (rc != OVC_OK) return rc;
+        }
     }
 
     AttnParams p{};
@@ -831,14 +961,15 @@ int launch_attention(const void* q8, const void* k8, const void* v_packed, const
     p.mid_window = mid_window_blocks;
     p.scale_log2 = static_cast<float>(static_cast<double>(softmax_scale) * 1.4426950408889634);
 
-    const size_t smem_bytes = sizeof(SmemLayout) + 1024;
+    const size_t smem_vs = sizeof(SmemLayout) + 1024, smem_plain = offsetof(SmemLayout, means) + 1024;
+    const size_t smem_bytes = vs_means != nullptr ? smem_vs : smem_plain;
     static std::atomic<bool> configured[64];
     if (device < 64 && !configured[device].load(std::memory_order_acquire)) {
-        err = cudaFuncSetAttribute(attention_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem_bytes));
+        err = cudaFuncSetAttribute(attention_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem_plain));
         if (err == cudaSuccess)
-            err = cudaFuncSetAttribute(attention_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem_bytes));
+            err = cudaFuncSetAttribute(attention_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem_vs));
         if (err == cudaSuccess)
-            err = cudaFuncSetAttribute(attention_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem_bytes));
+            err = cudaFuncSetAttribute(attention_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem_plain));
         if (err != cudaSuccess) { set_last_cuda_error(err); return OVC_ERR_CUDA; }
         configured[device].store(true, std::memory_order_release);
     }
@@ -849,9 +980,16 @@ int launch_attention(const void* q8, const void* k8, const void* v_packed, const
         err = cudaMemsetAsync(status, 0, sizeof(uint32_t), s);
         if (err != cudaSuccess) { set_last_cuda_error(err); return OVC_ERR_CUDA; }
     }
-    if (vs_means != nullptr) attention_kernel<true, false><<<grid, kThreads, smem_bytes, s>>>(map_q, map_k, map_v, p);
-    else if (causal) attention_kernel<false, true><<<grid, kThreads, smem_bytes, s>>>(map_q, map_k, map_v, p);
-    else attention_kernel<false, false><<<grid, kThreads, smem_bytes, s>>>(map_q, map_k, map_v, p);
+    if (vs_means != nullptr) {
+        const int n_groups = static_cast<int>(ceil_div(n_tiles, kMeanGroup));
+        means_split_kernel<<<dim3(n_groups, static_cast<unsigned>(H)), kDim, 0, s>>>(
+            vs_means, static_cast<uint4*>(vs_workspace), static_cast<int>(n_tiles), static_cast<int>(H), n_groups);
+        attention_kernel<true, false><<<grid, kThreads, smem_bytes, s>>>(map_q, map_k, map_v, map_m, p);
+    } else if (causal) {
+        attention_kernel<false, true><<<grid, kThreads, smem_bytes, s>>>(map_q, map_k, map_v, map_m, p);
+    } else {
+        attention_kernel<false, false><<<grid, kThreads, smem_bytes, s>>>(map_q, map_k, map_v, map_m, p);
+    }
     return check_launch();
 }
 
@@ -874,7 +1012,7 @@ extern "C" int ovc_attention(const void* q8, const void* k8, const void* v_packe
                              int64_t repair_rows, void* out, int64_t B, int64_t Sq, int64_t Sk, int64_t H,
                              float softmax_scale, int mid_window_blocks, uint32_t* status, void* stream) {
     return launch_attention(q8, k8, v_packed, q_descale, q_blocks, k_descale, v_descale, repair_kd, repair_rows, nullptr,
-                            nullptr, out, nullptr, 0, B, Sq, Sk, H, softmax_scale, mid_window_blocks, status, stream);
+                            nullptr, nullptr, out, nullptr, 0, B, Sq, Sk, H, softmax_scale, mid_window_blocks, status, stream);
 }
 
 extern "C" int ovc_attention_ex(const void* q8, const void* k8, const void* v_packed, const float* q_descale,
@@ -882,16 +1020,21 @@ extern "C" int ovc_attention_ex(const void* q8, const void* k8, const void* v_pa
                                 int64_t repair_rows, void* out, float* lse, int causal, int64_t B, int64_t Sq, int64_t Sk,
                                 int64_t H, float softmax_scale, int mid_window_blocks, uint32_t* status, void* stream) {
     return launch_attention(q8, k8, v_packed, q_descale, q_blocks, k_descale, v_descale, repair_kd, repair_rows, nullptr,
-                            nullptr, out, lse, causal, B, Sq, Sk, H, softmax_scale, mid_window_blocks, status, stream);
+                            nullptr, nullptr, out, lse, causal, B, Sq, Sk, H, softmax_scale, mid_window_blocks, status, stream);
+}
+
+extern "C" int64_t ovc_attention_vsmooth_workspace(int64_t Sk, int64_t H) {
+    if (Sk < 1 || H < 1) return 0;
+    return ceil_div(ceil_div(Sk, kTile), kMeanGroup) * 128 * kDim * H;
 }
 
 extern "C" int ovc_attention_vsmooth(const void* q8, const void* k8, const void* v_packed, const float* unit_descale,
-                                     const float* means, const float* channel_scale, void* out, int64_t Sq, int64_t Sk,
-                                     int64_t H, float softmax_scale, int mid_window_blocks, uint32_t* status,
-                                     void* stream) {
+                                     const float* means, const float* channel_scale, void* workspace, void* out,
+                                     int64_t Sq, int64_t Sk, int64_t H, float softmax_scale, int mid_window_blocks,
+                                     uint32_t* status, void* stream) {
     if (!means || !channel_scale || !unit_descale || !aligned16(means) || !aligned16(channel_scale)) return OVC_ERR_ARGUMENT;
     const int64_t blocks = ceil_div(Sq > Sk ? Sq : Sk, kTile);
     // unit_descale: at least H * ceil(max(Sq,Sk)/128) floats equal to 1.0 (no Q/K/V descales on this path).
     return launch_attention(q8, k8, v_packed, unit_descale, blocks, unit_descale, unit_descale, nullptr, 0, means,
-                            channel_scale, out, nullptr, 0, 1, Sq, Sk, H, softmax_scale, mid_window_blocks, status, stream);
+                            channel_scale, workspace, out, nullptr, 0, 1, Sq, Sk, H, softmax_scale, mid_window_blocks, status, stream);
 }

@@ -125,6 +125,11 @@ __device__ __forceinline__ uint32_t tmem_ld1(uint32_t taddr) {
 __device__ __forceinline__ void tmem_st1(uint32_t taddr, uint32_t r) {
     asm volatile("tcgen05.st.sync.aligned.32x32b.x1.b32 [%0], {%1};" ::"r"(taddr), "r"(r) : "memory");
 }
+__device__ __forceinline__ void tmem_st8(uint32_t taddr, const uint32_t* r) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"r"(taddr), "r"(r[0]),
+                 "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
+                 : "memory");
+}
 
 // ---- tcgen05 MMA, FP8 E4M3 x E4M3 -> FP32, one CTA -------------------------------------------
 // Four K-steps of one 128-wide MMA, issued by one elected lane while the whole warp executes the
@@ -170,6 +175,18 @@ __device__ __forceinline__ void mma4_f8_ts(uint32_t d_tmem, uint32_t a_tmem, uin
         : "r"(d_tmem), "r"(a_tmem), "r"(b_lo), "r"(kSmemDescHi), "r"(idesc), "r"(accumulate_first)
         : "memory");
 }
+// One BF16 x BF16 -> FP32 product of depth 16 added to the accumulator: A = 8 columns of tensor memory (two
+// BF16 values per column), B = 32 bytes of each 128-byte row of a swizzled shared-memory tile.
+__device__ __forceinline__ void mma_bf16_ts(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo, uint32_t idesc) {
+    asm volatile(
+        "{\n\t.reg .pred leader;\n\t.reg .b64 db;\n\t"
+        "elect.sync _|leader, 0xFFFFFFFF;\n\t"
+        "mov.b64 db, {%2, %3};\n\t"
+        "@leader tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, 1;\n\t}"
+        :
+        : "r"(d_tmem), "r"(a_tmem), "r"(b_lo), "r"(kSmemDescHi), "r"(idesc)
+        : "memory");
+}
 __device__ __forceinline__ void mma_commit_elect(uint32_t bar) {
     asm volatile(
         "{\n\t.reg .pred leader;\n\t"
@@ -183,6 +200,15 @@ __device__ __forceinline__ void mma_commit_elect(uint32_t bar) {
 __host__ __device__ constexpr uint32_t idesc_e4m3_f32(int n) {
     return (1u << 4)                              // accumulator format F32
            | (0u << 7) | (0u << 10)               // A, B format E4M3
+           | (0u << 15) | (0u << 16)              // A, B K-major
+           | (static_cast<uint32_t>(n >> 3) << 17)  // N / 8
+           | (static_cast<uint32_t>(128 >> 4) << 24);  // M / 16
+}
+
+// Instruction descriptor for kind::f16, BF16 x BF16 -> F32, both operands K-major, M = 128.
+__host__ __device__ constexpr uint32_t idesc_bf16_f32(int n) {
+    return (1u << 4)                              // accumulator format F32
+           | (1u << 7) | (1u << 10)               // A, B format BF16
            | (0u << 15) | (0u << 16)              // A, B K-major
            | (static_cast<uint32_t>(n >> 3) << 17)  // N / 8
            | (static_cast<uint32_t>(128 >> 4) << 24);  // M / 16

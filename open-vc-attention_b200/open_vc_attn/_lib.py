@@ -39,7 +39,8 @@ SIGNATURES = {
     "ovc_vs_block_stats": (_i, [_p, _p, _p, _p, _l, _l, _p]),
     "ovc_vs_block_write": (_i, [_p, _p, _p, _p, _p, _p, _p, _p, _p, _l, _l, _p]),
     "ovc_cast_e4m3": (_i, [_p, _i, _p, _l, _p]),
-    "ovc_attention_vsmooth": (_i, [_p, _p, _p, _p, _p, _p, _p, _l, _l, _l, _f, _i, _p, _p]),
+    "ovc_attention_vsmooth_workspace": (_l, [_l, _l]),
+    "ovc_attention_vsmooth": (_i, [_p, _p, _p, _p, _p, _p, _p, _p, _l, _l, _l, _f, _i, _p, _p]),
 }
 
 _lib = None

@@ -305,16 +305,17 @@ def _v_smooth_forward(q, k, v, means, scale, softmax_scale, mid_window_blocks, d
         scale = scale.contiguous()
         ones = _unit_descale(device, heads * ((max(sq, sk) + 127) // 128))
         out = torch.empty(q.shape, dtype=torch.bfloat16, device=device)
+        workspace = torch.empty(lib.ovc_attention_vsmooth_workspace(sk, heads), dtype=torch.uint8, device=device)
         _lib.check(
             lib.ovc_attention_vsmooth(
                 q.data_ptr(), k.data_ptr(), packed.data_ptr(), ones.data_ptr(), means.data_ptr(), scale.data_ptr(),
-                out.data_ptr(), sq, sk, heads, float(softmax_scale), window, status_word(device).data_ptr(),
+                workspace.data_ptr(), out.data_ptr(), sq, sk, heads, float(softmax_scale), window, status_word(device).data_ptr(),
                 _lib.stream_pointer(device),
             ),
             "ovc_attention_vsmooth",
         )
         _publish_status(device)
-        del packed
+        del packed, workspace
     return out
 
 

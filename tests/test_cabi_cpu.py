@@ -72,8 +72,14 @@ def test_null_and_bad_arguments_are_rejected_without_a_gpu(lib):
     assert lib.ovc_attention_ex(null, null, null, null, 1, null, null, null, 0, null, null, 0, 1, 128, 128, 1, 0.1, -1, null, null) == bad
     assert lib.ovc_attention_ex(p, p, p, p, 1, p, p, null, 0, p, null, 1, 1, 128, 128, 1, 0.1, 4, null, null) == bad   # causal + window
     assert lib.ovc_attention_ex(p, p, p, p, 1, p, p, p, 128, p, null, 1, 1, 128, 256, 1, 0.1, -1, null, null) == bad   # causal + repair
-    assert lib.ovc_attention_vsmooth(p, p, p, p, null, p, p, 128, 128, 1, 0.1, -1, null, null) == bad                   # no means
-    assert lib.ovc_attention_vsmooth(p, p, p, p, p + 4, p, p, 128, 128, 1, 0.1, -1, null, null) == bad                  # misaligned means
+    assert lib.ovc_attention_vsmooth(p, p, p, p, null, p, p, p, 128, 128, 1, 0.1, -1, null, null) == bad                # no means
+    assert lib.ovc_attention_vsmooth(p, p, p, p, p + 4, p, p, p, 128, 128, 1, 0.1, -1, null, null) == bad               # misaligned means
+    assert lib.ovc_attention_vsmooth(p, p, p, p, p, p, null, p, 128, 128, 1, 0.1, -1, null, null) == bad                # no workspace
+    assert lib.ovc_attention_vsmooth(p, p, p, p, p, p, p + 4, p, 128, 128, 1, 0.1, -1, null, null) == bad               # misaligned workspace
+    # one 128-byte row per (head, channel) and group of 32 key blocks
+    assert lib.ovc_attention_vsmooth_workspace(73397, 7) == 18 * 128 * 128 * 7
+    assert lib.ovc_attention_vsmooth_workspace(128, 1) == 128 * 128
+    assert lib.ovc_attention_vsmooth_workspace(0, 1) == 0
     assert lib.ovc_vs_assign(null, null, null, 128, 1, 8, null) == bad
     assert lib.ovc_vs_assign(p, p, p, 128, 1, 129, null) == bad            # more than 128 clusters
     assert lib.ovc_vs_assign(p, p, p, 4, 1, 8, null) == bad                # more clusters than tokens

@@ -159,6 +159,37 @@ def test_tails_and_scan_orders(s, h, window):
     assert oatt.relative_l2(f32(out), want) < ORACLE_TOL
 
 
+@pytest.mark.parametrize("s,h,window,exact_bf16_means", [(9000, 1, None, True), (9000, 2, 4, True), (4500, 1, 20, False),
+                                                         (6200, 1, None, False)])
+def test_long_scans_restore_means_on_the_tensor_core(s, h, window, exact_bf16_means):
+    """More than 16 key blocks: the masses of complete slices of sixteen blocks meet their means in BF16 tensor-core
+    products (several tiles of means, both scan orders); means that are not BF16 values keep 16 bits."""
+    _, baselines, forward, _ = _modules()
+    from open_vc_attn.api import raw_forward
+
+    q, k, v = structured_qkv(s, h, seed=3 * s + h)
+    prepared = baselines.prepare_vc(q, k, v, clusters=32, iterations=2)
+    kwargs = prepared.forward_kwargs()
+    means = prepared.means
+    if not exact_bf16_means:
+        means = means * 1.00173
+        kwargs = {key: (means if value is prepared.means else value) for key, value in kwargs.items()}
+        assert any(value is means for value in kwargs.values())
+    out, _ = raw_forward(prepared.q, prepared.k, prepared.v, expcast=True, mid_window_blocks=window, **kwargs)
+    forward.check_status(q.device)
+    blocks = (s + 127) // 128
+    m_blocks = [0, (blocks // 2) // 2, (blocks - 1) // 2]
+    ones = np.ones((h, blocks), dtype=np.float32)
+    want = oatt.expcast_attention(
+        u8(prepared.q), u8(prepared.k), u8(prepared.v), ones, ones, np.ones(h, dtype=np.float32), mid_window_blocks=window,
+        rows=m_blocks, v_smooth_means=f32(means).reshape(blocks, h, 128), v_channel_scale=f32(prepared.scale).reshape(h, 128),
+    )
+    rows = np.concatenate([np.arange(256 * m, min(256 * m + 256, s)) for m in m_blocks])
+    error = oatt.relative_l2(f32(out)[rows], want[rows])
+    print(f"S={s} H={h} window={window}: rel-L2 vs oracle {error:.2e}")
+    assert error < ORACLE_TOL
+
+
 def test_reuse_path_is_graph_capturable():
     # tests/gpu/test_attention.py:128-150 of the reference
     _, baselines, _, _ = _modules()
