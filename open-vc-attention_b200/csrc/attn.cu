@@ -25,8 +25,10 @@
 //
 // Tensor memory map (512 columns): S 0..127 (shared by both stages), P0 128..159, P1 160..191,
 // O0 192..327, O1 328..463; each O region is 128 output columns followed by 8 copies of the
-// denominator (the PV product has N = 136).  The V-Smooth variant also uses W0 464..479 and W1 480..495:
-// per stage the probability masses of sixteen key blocks as BF16 high parts (8 columns) and low parts (8).
+// denominator (the PV product has N = 136).  V-Smooth variant: O0 192..335, O1 336..479, each 128 output
+// columns followed by 16 columns that collect the probability masses of sixteen key blocks one by one (N = 144:
+// the extension of a V tile is one row of ones, row = key block mod 16), and W0 480..495, W1 496..511: those
+// masses as BF16 high parts (8 columns) and low parts (8), the A operand of the products with the block means.
 
 #include <atomic>
 
@@ -46,19 +48,21 @@ constexpr int kThreads = 384;
 constexpr int kKStages = 4;
 constexpr int kVStages = 4;
 constexpr int kTileBytes = kTile * kDim;          // 16384: one FP8 tile, 128 rows of 128 bytes
-constexpr int kOnesRows = 8;                      // extension of the PV product that sums P
-constexpr int kVSlotBytes = kTileBytes + kOnesRows * 128;
-constexpr int kPvN = kDim + kOnesRows;            // 136
-constexpr uint32_t kColS = 0, kColP = 128, kColO = 192, kColOStride = kPvN, kColW = 464, kTmemCols = 512;
 constexpr int kMeanGroup = 32;                    // key blocks per tile of block means (V-Smooth)
 constexpr int kMeanSlice = 16;                    // key blocks restored by one group of BF16 products
+// Rows appended to a V tile so that the PV product also sums P: 8 rows of ones (one denominator, 8 copies), or for
+// V-Smooth 16 rows of which one holds ones (a denominator per key block of a slice).
+__host__ __device__ constexpr int ext_rows(bool vs) { return vs ? kMeanSlice : 8; }
+__host__ __device__ constexpr int pv_n(bool vs) { return kDim + ext_rows(vs); }  // 136 / 144
+constexpr uint32_t kColS = 0, kColP = 128, kColO = 192, kColW = 480, kTmemCols = 512;
 constexpr long long kWaitCycles = 400000000LL;    // bounded barrier wait (~0.2 s)
 constexpr uint32_t kSleepHintNs = 100000;         // one hardware-suspended try_wait lasts at most this
 
+template <bool kVS>
 struct SmemLayout {
     alignas(1024) uint8_t q[2][kTileBytes];
     alignas(1024) uint8_t k[kKStages][kTileBytes];
-    alignas(1024) uint8_t v[kVStages][kVSlotBytes];
+    alignas(1024) uint8_t v[kVStages][kTileBytes + ext_rows(kVS) * 128];
     alignas(8) uint64_t q_full[2];
     uint64_t k_full[kKStages], v_full[kVStages];
     uint64_t k_empty[kKStages], v_empty[kVStages];  // slot may be refilled (one arrival by a stage-1 thread)
@@ -70,9 +74,9 @@ struct SmemLayout {
     uint64_t m_full[2], m_free[2];  // V-Smooth: a tile of block means has landed / its last reader is done (commit)
     uint32_t tmem_base;
     volatile uint32_t abort_flag;
-    // V-Smooth only (the other variants do not allocate it): two tiles of block means, 128 channels x 128 bytes
-    // = BF16 high parts of 32 key blocks, then their low parts, in the 128-byte swizzle.
-    alignas(1024) uint8_t means[2][kTileBytes];
+    // V-Smooth only (a stub in the other variants): two tiles of block means, 128 channels x 128 bytes = BF16 high
+    // parts of 32 key blocks, then their low parts, in the 128-byte swizzle.
+    alignas(1024) uint8_t means[kVS ? 2 : 1][kVS ? kTileBytes : 16];
 };
 
 struct AttnParams {
@@ -132,7 +136,8 @@ __device__ __forceinline__ bool wait_bar(volatile uint32_t* abort_flag, uint64_t
     }
 }
 
-__device__ __forceinline__ bool wait_bar(SmemLayout& sm, uint64_t* bar, uint32_t parity, uint32_t* status) {
+template <class Layout>
+__device__ __forceinline__ bool wait_bar(Layout& sm, uint64_t* bar, uint32_t parity, uint32_t* status) {
     return wait_bar(&sm.abort_flag, bar, parity, status, kWaitCycles);
 }
 
@@ -246,7 +251,8 @@ __device__ __forceinline__ uint32_t bf16x2(float lo, float hi) {
 }
 
 // After a failed wait: let the MMAs this thread has issued finish (bounded) before tensor memory is released.
-__device__ __forceinline__ void drain_mmas(SmemLayout& sm, int which) {
+template <class Layout>
+__device__ __forceinline__ void drain_mmas(Layout& sm, int which) {
     mma_commit_elect(smem_addr(&sm.drain[which]));
     const long long t0 = clock64();
     while (!mbar_try_wait(smem_addr(&sm.drain[which]), 0) && clock64() - t0 < kWaitCycles) {}
@@ -267,13 +273,24 @@ __device__ __forceinline__ void poison_row(const AttnParams& p, int batch, int h
 // kVS: V-Smooth variant (VC-Attention baseline): V holds residual codes; every key step adds
 // (sum of the tile's probabilities) x (the tile's block mean) to the accumulator, and the output is
 // scaled per channel (cute/flash_fwd_sm100.py:4857-4863 of the reference).
+// The tensor map of the block means is a kernel parameter of the V-Smooth variant only.
+template <bool kVS>
+struct MeansMap {
+    CUtensorMap map;
+};
+template <>
+struct MeansMap<false> {
+    int unused;
+};
+
 template <bool kVS, bool kCausal>
 __global__ void __launch_bounds__(kThreads, 1)
 attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
-                 const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_m,
+                 const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ MeansMap<kVS> means_map,
                  const AttnParams p) {
     extern __shared__ uint8_t smem_raw[];
-    SmemLayout& sm = *reinterpret_cast<SmemLayout*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    using Layout = SmemLayout<kVS>;
+    Layout& sm = *reinterpret_cast<Layout*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int m_block = blockIdx.x % p.m_blocks;
@@ -332,9 +349,10 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         mbar_init_fence();
     }
     // Rows 128.. of every V slot: E4M3 1.0, so PV also accumulates the row sums of P.
-    for (int i = threadIdx.x; i < kVStages * kOnesRows * 128 / 4; i += kThreads) {
-        const int slot = i / (kOnesRows * 128 / 4), w = i % (kOnesRows * 128 / 4);
-        reinterpret_cast<uint32_t*>(&sm.v[slot][kTileBytes])[w] = 0x38383838u;
+    // (V-Smooth: all zero; the relay sets the row of the tile that has landed.)
+    for (int i = threadIdx.x; i < kVStages * ext_rows(kVS) * 128 / 4; i += kThreads) {
+        const int slot = i / (ext_rows(kVS) * 128 / 4), w = i % (ext_rows(kVS) * 128 / 4);
+        reinterpret_cast<uint32_t*>(&sm.v[slot][kTileBytes])[w] = kVS ? 0u : 0x38383838u;
     }
     fence_proxy_async_smem();
     if (warp == 9) {
@@ -370,7 +388,8 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
                         const int b = issued_m & 1;
                         if (issued_m >= 2 && !wait_bar(sm, &sm.m_free[b], ((issued_m >> 1) - 1) & 1, p.status)) break;
                         mbar_expect_tx(smem_addr(&sm.m_full[b]), kTileBytes);
-                        tma_load_4d(smem_addr(sm.means[b]), &tmap_m, smem_addr(&sm.m_full[b]), (j / kMeanGroup) * 128, 0, head, 0, keep);
+                        if constexpr (kVS)
+                            tma_load_4d(smem_addr(sm.means[b]), &means_map.map, smem_addr(&sm.m_full[b]), (j / kMeanGroup) * 128, 0, head, 0, keep);
                         ++issued_m;
                     }
                     j_before = j;
@@ -450,7 +469,8 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         } else if (warp == 11) {
             // ---------------- PV issuer ----------------
             // p_full[s] completion n: stage s has stored P_s(n) and V(n) has landed.
-            constexpr uint32_t idesc_pv = idesc_e4m3_f32(kPvN);
+            constexpr uint32_t idesc_pv = idesc_e4m3_f32(pv_n(kVS));
+            constexpr uint32_t kColOStride = pv_n(kVS);
             constexpr uint32_t idesc_mean = idesc_bf16_f32(kDim);
             bool ok = true;
             int groups_left = 0;  // V-Smooth: groups of block means the scan has left (buffer groups_left & 1 is current)
@@ -500,6 +520,22 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
                     mbar_arrive(smem_addr(&sm.gate[1]));
                     if (n > 0 && !wait_bar(sm, &sm.p_full[0], (n - 1) & 1, p.status)) break;
                     if (!wait_bar(sm, &sm.v_full[n % kVStages], (n / kVStages) & 1, p.status)) break;
+                    if (kVS) {
+                        // Row (key block mod 16) of the slot's extension holds ones, the others zeros: clear the row
+                        // of the tile that used the slot before (its products are long done), set this tile's, and
+                        // publish to the async proxy before the arrival that lets the first PV with this tile start.
+                        uint4* ext = reinterpret_cast<uint4*>(&sm.v[n % kVStages][kTileBytes]);
+                        if (n >= kVStages) {
+                            const int old_row = tile_at(n - kVStages, j0, p.first_tile, n_tiles) % kMeanSlice;
+#pragma unroll
+                            for (int i = 0; i < 8; ++i) ext[old_row * 8 + i] = make_uint4(0u, 0u, 0u, 0u);
+                        }
+                        const int row = tile_at(n, j0, p.first_tile, n_tiles) % kMeanSlice;
+#pragma unroll
+                        for (int i = 0; i < 8; ++i)
+                            ext[row * 8 + i] = make_uint4(0x38383838u, 0x38383838u, 0x38383838u, 0x38383838u);
+                        fence_proxy_async_smem();
+                    }
                     mbar_arrive(smem_addr(&sm.p_full[0]));
                 }
             }
@@ -511,7 +547,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         const int row_in_tile = (warp & 3) * 32 + lane;
         const uint32_t lane_base = tmem + (static_cast<uint32_t>((warp & 3) * 32) << 16);
         const uint32_t t_s = lane_base + kColS, t_p = lane_base + kColP + 32 * stage;
-        const uint32_t t_o = lane_base + kColO + stage * kColOStride;
+        const uint32_t t_o = lane_base + kColO + stage * pv_n(kVS);
         const int q_tile = 2 * m_block + stage;
         const long long bh_l = static_cast<long long>(batch) * p.H + head;
         const float qd = q_tile < p.q_blocks ? __ldg(p.q_descale + bh_l * p.q_blocks + q_tile) : 1.0f;
@@ -522,13 +558,8 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         const uint32_t my_gate = smem_addr(&sm.gate[stage]);  // "scores copied out"
 
         float row_max = 0.0f, bias = 0.0f, saved_denominator = 0.0f;
-        float l_known = 0.0f;  // V-Smooth: denominator before the previous step's PV, after rescaling
-        int j_prev = 0;        // V-Smooth: key tile of the previous step
-        // V-Smooth: probability masses of the key blocks of the current slice (slot = block % 16) whose means
-        // have not been added to the accumulator yet, in the accumulator's current scale.
-        float mass[kVS ? kMeanSlice : 1];
-#pragma unroll
-        for (int i = 0; i < (kVS ? kMeanSlice : 1); ++i) mass[i] = 0.0f;
+        float l_closed = 0.0f;  // V-Smooth: denominator of the slices already closed, in the accumulator's scale
+        int j_prev = 0;         // V-Smooth: key tile of the previous step
         const uint32_t t_w = lane_base + kColW + 16 * stage;
         bool ok = true;
         for (int it = 0; it < n_iters; ++it) {
@@ -604,18 +635,40 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
             }
             tmem_st32(t_p, codes);
 
-            const bool rescale = it > 0 && __any_sync(0xFFFFFFFFu, alpha < 1.0f);
             if (kVS) {
+                const bool rescale = it > 0 && __any_sync(0xFFFFFFFFu, alpha < 1.0f);
                 if (it > 0) {
-                    // The previous PV has landed: its tile's probability sum is the growth of the denominator.  The
-                    // sum joins the pending masses; every pending mass follows the accumulator's rescaling.
-                    const float l_cur = __uint_as_float(tmem_ld1(t_o + kDim));
-                    tmem_wait_ld();
-                    const float w = l_cur - l_known;
-                    const int slot = j_prev % kMeanSlice;
+                    // The sixteen mass columns hold the probability sums of the current slice's key blocks (the tensor
+                    // core wrote them, one block per column).  When the previous step closed the slice, its masses
+                    // go to the W columns as BF16 high and low parts - the PV issuer adds masses x block means to the
+                    // accumulator before this step's PV - and the columns start again from zero.
+                    const bool slice_closed = j_prev % kMeanSlice == 0;
+                    l_closed *= alpha;
+                    if (slice_closed || rescale) {
+                        uint32_t m[kMeanSlice];
+                        tmem_ld16(t_o + kDim, m);
+                        tmem_wait_ld();
+                        float sum = 0.0f;
 #pragma unroll
-                    for (int i = 0; i < kMeanSlice; ++i) mass[i] = (i == slot ? w : mass[i]) * alpha;
-                    l_known = l_cur * alpha;
+                        for (int i = 0; i < kMeanSlice; ++i) {
+                            m[i] = __float_as_uint(__uint_as_float(m[i]) * alpha);
+                            sum += __uint_as_float(m[i]);
+                        }
+                        if (slice_closed) {
+                            l_closed += sum;
+                            uint32_t hi[8], lo[8];
+#pragma unroll
+                            for (int i = 0; i < 8; ++i) {
+                                const float a = __uint_as_float(m[2 * i]), b = __uint_as_float(m[2 * i + 1]);
+                                hi[i] = bf16x2(a, b);
+                                lo[i] = bf16x2(a - __uint_as_float(hi[i] << 16), b - __uint_as_float(hi[i] & 0xFFFF0000u));
+                                m[2 * i] = 0u, m[2 * i + 1] = 0u;
+                            }
+                            tmem_st8(t_w, hi);
+                            tmem_st8(t_w + 8, lo);
+                        }
+                        tmem_st16(t_o + kDim, m);
+                    }
                     if (rescale) {
 #pragma unroll
                         for (int c = 0; c < 4; ++c) {
@@ -626,26 +679,12 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
                             for (int e = 0; e < 32; ++e) o[e] = __float_as_uint(__uint_as_float(o[e]) * alpha);
                             tmem_st32(t_o + 32 * c, o);
                         }
-                        tmem_st1(t_o + kDim, __float_as_uint(l_known));
-                    }
-                    if (slot == 0) {
-                        // The slice is complete: hand its masses to the tensor core as BF16 high and low parts
-                        // (the PV issuer adds masses x block means to the accumulator before this step's PV).
-                        uint32_t hi[8], lo[8];
-#pragma unroll
-                        for (int i = 0; i < 8; ++i) {
-                            hi[i] = bf16x2(mass[2 * i], mass[2 * i + 1]);
-                            lo[i] = bf16x2(mass[2 * i] - __uint_as_float(hi[i] << 16),
-                                           mass[2 * i + 1] - __uint_as_float(hi[i] & 0xFFFF0000u));
-                            mass[2 * i] = 0.0f, mass[2 * i + 1] = 0.0f;
-                        }
-                        tmem_st8(t_w, hi);
-                        tmem_st8(t_w + 8, lo);
                     }
                 }
                 j_prev = j;
             } else {
                 const bool first_repair = p.first_tile > 0 && j == p.first_tile - 1;
+                const bool rescale = it > 0 && __any_sync(0xFFFFFFFFu, alpha < 1.0f);
                 if (first_repair) {
                     // First repair tile: the denominator holds the original tokens' total only.
                     saved_denominator = __uint_as_float(tmem_ld1(t_o + kDim));
@@ -674,13 +713,21 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         if (ok) ok = __all_sync(0xFFFFFFFFu, wait_bar(sm, &sm.o_full[stage], 0, p.status));
         if (ok) {
             tc_fence_after();
-            float l = __uint_as_float(tmem_ld1(t_o + kDim));
-            tmem_wait_ld();
+            float l;
+            float mass[kVS ? kMeanSlice : 1];  // V-Smooth: masses of the last slice (block = slice_first + column)
             if (kVS) {
-                const float w_last = l - l_known;  // probability sum of the last tile
+                uint32_t m[kMeanSlice];
+                tmem_ld16(t_o + kDim, m);
+                tmem_wait_ld();
+                l = l_closed;
 #pragma unroll
-                for (int i = 0; i < kMeanSlice; ++i)
-                    if (i == j_prev % kMeanSlice) mass[i] = w_last;
+                for (int i = 0; i < kMeanSlice; ++i) {
+                    mass[i] = __uint_as_float(m[i]);
+                    l += mass[i];
+                }
+            } else {
+                l = __uint_as_float(tmem_ld1(t_o + kDim));
+                tmem_wait_ld();
             }
             if (p.first_tile > 0) l = saved_denominator;
             const bool bad = l == 0.0f || l != l;
@@ -924,7 +971,8 @@ int launch_attention(const void* q8, const void* k8, const void* v_packed, const
     if (err != cudaSuccess) { set_last_cuda_error(err); return OVC_ERR_CUDA; }
     if (major != 10 || minor != 0) return OVC_ERR_UNSUPPORTED;  // the library holds sm_100a code only
 
-    CUtensorMap map_q, map_k, map_v, map_m;
+    CUtensorMap map_q, map_k, map_v;
+    MeansMap<true> map_m{};
     {
         const cuuint64_t dq[4] = {128, static_cast<cuuint64_t>(H), static_cast<cuuint64_t>(Sq), static_cast<cuuint64_t>(B)};
         const cuuint64_t sq[3] = {128, static_cast<cuuint64_t>(H) * 128, static_cast<cuuint64_t>(Sq) * H * 128};
@@ -940,13 +988,12 @@ int launch_attention(const void* q8, const void* k8, const void* v_packed, const
                                   static_cast<cuuint64_t>(Sk_pad) * 128 * H};
         rc = make_map(&map_v, v_packed, dv, sv, 128, 128, 1);
         if (rc != OVC_OK) return rc;
-        map_m = map_q;  // not read unless V-Smooth
         if (vs_means != nullptr) {
             // Rows of n_groups x 128 bytes per (head, channel): see means_split_kernel.
             const cuuint64_t row_bytes = static_cast<cuuint64_t>(ceil_div(n_tiles, kMeanGroup)) * 128;
             const cuuint64_t dm[4] = {row_bytes, 128, static_cast<cuuint64_t>(H), 1};
             const cuuint64_t sm_[3] = {row_bytes, row_bytes * 128, row_bytes * 128 * H};
-            rc = make_map(&map_m, vs_workspace, dm, sm_, 128, 128, 1);
+            rc = make_map(&map_m.map, vs_workspace, dm, sm_, 128, 128, 1);
             if (rc != OVC_OK) return rc;
         }
     }
@@ -961,7 +1008,7 @@ int launch_attention(const void* q8, const void* k8, const void* v_packed, const
     p.mid_window = mid_window_blocks;
     p.scale_log2 = static_cast<float>(static_cast<double>(softmax_scale) * 1.4426950408889634);
 
-    const size_t smem_vs = sizeof(SmemLayout) + 1024, smem_plain = offsetof(SmemLayout, means) + 1024;
+    const size_t smem_vs = sizeof(SmemLayout<true>) + 1024, smem_plain = sizeof(SmemLayout<false>) + 1024;
     const size_t smem_bytes = vs_means != nullptr ? smem_vs : smem_plain;
     static std::atomic<bool> configured[64];
     if (device < 64 && !configured[device].load(std::memory_order_acquire)) {
@@ -986,9 +1033,9 @@ int launch_attention(const void* q8, const void* k8, const void* v_packed, const
             vs_means, static_cast<uint4*>(vs_workspace), static_cast<int>(n_tiles), static_cast<int>(H), n_groups);
         attention_kernel<true, false><<<grid, kThreads, smem_bytes, s>>>(map_q, map_k, map_v, map_m, p);
     } else if (causal) {
-        attention_kernel<false, true><<<grid, kThreads, smem_bytes, s>>>(map_q, map_k, map_v, map_m, p);
+        attention_kernel<false, true><<<grid, kThreads, smem_bytes, s>>>(map_q, map_k, map_v, MeansMap<false>{}, p);
     } else {
-        attention_kernel<false, false><<<grid, kThreads, smem_bytes, s>>>(map_q, map_k, map_v, map_m, p);
+        attention_kernel<false, false><<<grid, kThreads, smem_bytes, s>>>(map_q, map_k, map_v, MeansMap<false>{}, p);
     }
     return check_launch();
 }
