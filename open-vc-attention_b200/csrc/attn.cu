@@ -270,9 +270,10 @@ __device__ __forceinline__ void poison_row(const AttnParams& p, int batch, int h
     if (p.lse != nullptr) p.lse[(static_cast<long long>(batch) * p.H + head) * p.Sq + row] = -INFINITY;
 }
 
-// kVS: V-Smooth variant (VC-Attention baseline): V holds residual codes; every key step adds
-// (sum of the tile's probabilities) x (the tile's block mean) to the accumulator, and the output is
-// scaled per channel (cute/flash_fwd_sm100.py:4857-4863 of the reference).
+// kVS: V-Smooth variant (VC-Attention baseline): V holds residual codes; (sum of a key block's probabilities) x
+// (the block's mean) is added to the accumulator for sixteen key blocks at a time by BF16 tensor-core products
+// (cute/flash_fwd_sm100.py:4111-4206,4482-4526 of the reference), and the output is scaled per channel
+// (cute/flash_fwd_sm100.py:4857-4863).
 // The tensor map of the block means is a kernel parameter of the V-Smooth variant only.
 template <bool kVS>
 struct MeansMap {
