@@ -284,7 +284,7 @@ struct MeansMap<false> {
     int unused;
 };
 
-template <bool kVS, bool kCausal>
+template <bool kVS, bool kCausal, bool kRepair>
 __global__ void __launch_bounds__(kThreads, 1)
 attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                  const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ MeansMap<kVS> means_map,
@@ -595,7 +595,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
                         if (c >= visible_columns) s[c] = 0xFF800000u;  // -inf
                 }
             }
-            if (j < p.first_tile) {
+            if (kRepair && j < p.first_tile) {
                 // Repair keys come from different K blocks: each column carries its own K descale.
                 const float4* kd4 = reinterpret_cast<const float4*>(p.repair_kd + static_cast<long long>(head) * p.first_tile * kTile + j * kTile);
 #pragma unroll
@@ -671,7 +671,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
                         tmem_st16(t_o + kDim, m);
                     }
                     if (rescale) {
-#pragma unroll
+#pragma unroll 1
                         for (int c = 0; c < 4; ++c) {
                             uint32_t o[32];
                             tmem_ld32(t_o + 32 * c, o);
@@ -684,7 +684,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
                 }
                 j_prev = j;
             } else {
-                const bool first_repair = p.first_tile > 0 && j == p.first_tile - 1;
+                const bool first_repair = kRepair && j == p.first_tile - 1;
                 const bool rescale = it > 0 && __any_sync(0xFFFFFFFFu, alpha < 1.0f);
                 if (first_repair) {
                     // First repair tile: the denominator holds the original tokens' total only.
@@ -693,7 +693,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
                 }
                 if (rescale) {
                     // The running max moved: rescale the accumulator and the denominator in place.
-#pragma unroll
+#pragma unroll 1
                     for (int c = 0; c < 4; ++c) {
                         uint32_t o[32];
                         tmem_ld32(t_o + 32 * c, o);
@@ -730,7 +730,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
                 l = __uint_as_float(tmem_ld1(t_o + kDim));
                 tmem_wait_ld();
             }
-            if (p.first_tile > 0) l = saved_denominator;
+            if (kRepair) l = saved_denominator;
             const bool bad = l == 0.0f || l != l;
             float inv;
             asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(inv) : "f"(bad ? 1.0f : l));
@@ -1013,11 +1013,13 @@ int launch_attention(const void* q8, const void* k8, const void* v_packed, const
     const size_t smem_bytes = vs_means != nullptr ? smem_vs : smem_plain;
     static std::atomic<bool> configured[64];
     if (device < 64 && !configured[device].load(std::memory_order_acquire)) {
-        err = cudaFuncSetAttribute(attention_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem_plain));
+        err = cudaFuncSetAttribute(attention_kernel<false, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem_plain));
         if (err == cudaSuccess)
-            err = cudaFuncSetAttribute(attention_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem_vs));
+            err = cudaFuncSetAttribute(attention_kernel<false, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem_plain));
         if (err == cudaSuccess)
-            err = cudaFuncSetAttribute(attention_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem_plain));
+            err = cudaFuncSetAttribute(attention_kernel<true, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem_vs));
+        if (err == cudaSuccess)
+            err = cudaFuncSetAttribute(attention_kernel<false, true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem_plain));
         if (err != cudaSuccess) { set_last_cuda_error(err); return OVC_ERR_CUDA; }
         configured[device].store(true, std::memory_order_release);
     }
@@ -1032,11 +1034,12 @@ int launch_attention(const void* q8, const void* k8, const void* v_packed, const
         const int n_groups = static_cast<int>(ceil_div(n_tiles, kMeanGroup));
         means_split_kernel<<<dim3(n_groups, static_cast<unsigned>(H)), kDim, 0, s>>>(
             vs_means, static_cast<uint4*>(vs_workspace), static_cast<int>(n_tiles), static_cast<int>(H), n_groups);
-        attention_kernel<true, false><<<grid, kThreads, smem_bytes, s>>>(map_q, map_k, map_v, map_m, p);
+        attention_kernel<true, false, false><<<grid, kThreads, smem_bytes, s>>>(map_q, map_k, map_v, map_m, p);
     } else if (causal) {
-        attention_kernel<false, true><<<grid, kThreads, smem_bytes, s>>>(map_q, map_k, map_v, MeansMap<false>{}, p);
+        attention_kernel<false, true, false><<<grid, kThreads, smem_bytes, s>>>(map_q, map_k, map_v, MeansMap<false>{}, p);
     } else {
-        attention_kernel<false, false><<<grid, kThreads, smem_bytes, s>>>(map_q, map_k, map_v, MeansMap<false>{}, p);
+        if (repair_rows > 0) attention_kernel<false, false, true><<<grid, kThreads, smem_bytes, s>>>(map_q, map_k, map_v, MeansMap<false>{}, p);
+        else attention_kernel<false, false, false><<<grid, kThreads, smem_bytes, s>>>(map_q, map_k, map_v, MeansMap<false>{}, p);
     }
     return check_launch();
 }
