@@ -214,6 +214,32 @@ def test_packed_sequences_are_attended_one_call_per_sequence():
     assert not torch.equal(whole[:129], alone[0])  # attending across the bound is a different result
 
 
+def test_diffusion_adapter_on_packed_sequences_and_padding(monkeypatch):
+    """The adapter of this package on the shapes, seed and checks of tests/gpu/test_attention.py:69-87 of the
+    reference: each packed sequence equals that sequence alone, trailing padding rows are zero."""
+    _api()
+    from open_vc_attn.integrations import DenseDiffusionAdapter
+
+    monkeypatch.setenv("OPEN_VC_ATTN_IMPLEMENTATION", "open-vc")
+    monkeypatch.setenv("OPEN_VC_ATTN_MODE", "expcast")
+    adapter = DenseDiffusionAdapter(2, 128, 128**-0.5)
+    torch.manual_seed(513)
+    q, k, v = [torch.randn(258, 2, 128, device=DEV, dtype=torch.bfloat16) for _ in range(3)]
+    bounds = (0, 129, 258)
+    cu = torch.tensor(bounds, device=DEV, dtype=torch.int32)
+    out = adapter.forward_varlen(q, k, v, cu_seqlens=cu, max_seqlen=129, cu_seqlens_host=bounds)
+    for a, b in zip(bounds, bounds[1:]):
+        assert torch.equal(out[a:b], adapter.forward(q[a:b], k[a:b], v[a:b]))
+    padded = DenseDiffusionAdapter(2, 128, 128**-0.5, packed_trailing_padding=True)
+    out = padded.forward_varlen(q, k, v, cu_seqlens=cu, max_seqlen=129, cu_seqlens_host=bounds)
+    assert torch.count_nonzero(out[129:]) == 0
+    assert torch.equal(out[:129], adapter.forward(q[:129], k[:129], v[:129]))
+    with pytest.raises(ValueError):
+        adapter.forward_varlen(q, k, v, cu_seqlens=cu, max_seqlen=129)
+    with pytest.raises(ValueError, match="reside with"):
+        adapter.forward_varlen(q, k, v, cu_seqlens=cu.cpu(), max_seqlen=129, cu_seqlens_host=bounds)
+
+
 @pytest.mark.parametrize("shape", [(300, 2), (2, 700, 3)])
 def test_log_sum_exp_output(shape):
     """return_lse=True: against the oracle's formula and against the exact log-sum-exp of the scaled scores."""

@@ -163,55 +163,149 @@ def test_gather_heads_with_two_gloo_ranks(heads):
     assert result[0] and result[1]
 
 
-REFERENCE_INTEGRATIONS = "/root/reference/src/open_vc_attn/integrations"
+def test_packed_bounds():
+    # tests/cpu/test_contracts.py:75-83 of the reference, and every fault segments() reports
+    from open_vc_attn.integrations import segments
+
+    assert segments((0, 129, 258), 258, 129) == [(0, 129, False), (129, 258, False)]
+    assert segments([0, 7], 7, 7) == [(0, 7, False)]
+    # one sequence and trailing padding: only with the option, only for two pieces, only if the first fills max_seqlen
+    assert segments((0, 129, 200), 200, 129, trailing_padding=True) == [(0, 129, False), (129, 200, True)]
+    assert segments((0, 129, 200), 200, 129) == [(0, 129, False), (129, 200, False)]
+    assert segments((0, 100, 200), 200, 129, trailing_padding=True) == [(0, 100, False), (100, 200, False)]
+    # padding may be longer than max_seqlen, a sequence may not
+    assert segments((0, 4, 20), 20, 4, trailing_padding=True)[1] == (4, 20, True)
+    for bounds, total, longest, text in [
+        (None, 9, 9, "cu_seqlens_host is required"),
+        ((0,), 0, 1, "start at zero"),
+        ((1, 9), 9, 9, "start at zero"),
+        ((0, 5, 8), 9, 9, "end at the tensor length"),
+        ((0, 5, 5, 9), 9, 9, "strictly increasing"),
+        ((0, 5.0, 9), 9, 9, "strictly increasing integers"),
+        ((0, 5, 9), 9, 4, "max_seqlen is inconsistent"),
+        ((0, 9), 9, 0, "max_seqlen is inconsistent"),
+    ]:
+        with pytest.raises(ValueError, match=text):
+            segments(bounds, total, longest)
 
 
-@pytest.mark.skipif(not os.path.isdir(REFERENCE_INTEGRATIONS), reason="needs a checkout of the reference beside this repository")
-def test_the_reference_adapter_runs_unchanged_on_this_package(monkeypatch):
-    """The reference's diffusion adapter (a caller of ``attention``) is not rebuilt here: its own source files,
-    loaded as ``open_vc_attn.integrations`` of THIS package, import, validate and dispatch per packed segment.
-    Nothing is copied; the files are read where they lie."""
-    import importlib
-    import types
-
-    import open_vc_attn
-
-    pytest.importorskip("torch")
-    package = types.ModuleType("open_vc_attn.integrations")
-    package.__path__ = [REFERENCE_INTEGRATIONS]
-    monkeypatch.setitem(sys.modules, "open_vc_attn.integrations", package)
-    for name in ("packed", "diffusion"):
-        monkeypatch.delitem(sys.modules, f"open_vc_attn.integrations.{name}", raising=False)
-    packed = importlib.import_module("open_vc_attn.integrations.packed")
-    diffusion = importlib.import_module("open_vc_attn.integrations.diffusion")
-    assert diffusion.__file__.startswith(REFERENCE_INTEGRATIONS)
-
-    # tests/cpu/test_contracts.py:75-83 of the reference
-    assert packed.segments((0, 129, 258), 258, 129) == [(0, 129, False), (129, 258, False)]
-    with pytest.raises(ValueError):
-        packed.segments((0, 5, 9), 9, 4)
+def test_diffusion_adapter_dispatches_per_sequence(monkeypatch):
+    """tests/gpu/test_attention.py:69-87 of the reference is the acceptance test on a GPU; here the host logic:
+    construction, environment selection, metadata checks, one attention() call per packed sequence."""
+    torch = pytest.importorskip("torch")
+    from open_vc_attn.integrations import DenseDiffusionAdapter, diffusion
 
     monkeypatch.delenv("OPEN_VC_ATTN_IMPLEMENTATION", raising=False)
     monkeypatch.delenv("OPEN_VC_ATTN_MODE", raising=False)
-    adapter = diffusion.DenseDiffusionAdapter(2, 128, 0.1)
-    assert (adapter.version, adapter.mode) == ("open-vc", "expcast")
+    adapter = DenseDiffusionAdapter(2, 128, 0.1)
+    assert (adapter.version, adapter.mode, adapter.scale, adapter.trailing_padding) == ("open-vc", "expcast", 0.1, False)
+    assert DenseDiffusionAdapter(2, 128, 0.1, num_kv_heads=2, prefix="blocks.0.attn").version == "open-vc"
     with pytest.raises(ValueError, match="head_size=128"):
-        diffusion.DenseDiffusionAdapter(2, 64, 0.1)
-    # per-segment dispatch: each packed sequence reaches this package's attention() on its own
-    import torch
+        DenseDiffusionAdapter(2, 64, 0.1)
+    with pytest.raises(ValueError, match="MHA"):
+        DenseDiffusionAdapter(8, 128, 0.1, num_kv_heads=2)
+    with pytest.raises(ValueError, match="noncausal"):
+        DenseDiffusionAdapter(2, 128, 0.1, causal=True)
+    with pytest.raises(ValueError, match="noncausal"):
+        DenseDiffusionAdapter(2, 128, 0.1, dropout_p=0.1)
+    monkeypatch.setenv("OPEN_VC_ATTN_MODE", "bf16")
+    with pytest.raises(ValueError, match="reference with bf16"):
+        DenseDiffusionAdapter(2, 128, 0.1)
+    # the reference's BF16 backend (a third-party package) is not part of this build: not a valid choice here
+    for version in ("reference", "fastest"):
+        monkeypatch.setenv("OPEN_VC_ATTN_IMPLEMENTATION", version)
+        with pytest.raises(ValueError, match="Invalid OPEN_VC_ATTN"):
+            DenseDiffusionAdapter(2, 128, 0.1)
+    monkeypatch.delenv("OPEN_VC_ATTN_IMPLEMENTATION")
+    monkeypatch.delenv("OPEN_VC_ATTN_MODE")
 
     calls = []
 
     def fake_attention(q, k, v, **options):
-        calls.append((tuple(q.shape), options["version"], options["mode"]))
-        return q.clone()
+        calls.append((tuple(q.shape), options["version"], options["mode"], options["softmax_scale"]))
+        return q + 1
 
     monkeypatch.setattr(diffusion, "attention", fake_attention)
     q = torch.zeros(258, 2, 128, dtype=torch.bfloat16)
     cu = torch.tensor([0, 129, 258], dtype=torch.int32)
     out = adapter.forward_varlen(q, q, q, cu_seqlens=cu, max_seqlen=129, cu_seqlens_host=(0, 129, 258))
-    assert out.shape == q.shape and calls == [((129, 2, 128), "open-vc", "expcast")] * 2
-    assert open_vc_attn.attention is not None
+    assert out.shape == q.shape and bool((out == 1).all())
+    assert calls == [((129, 2, 128), "open-vc", "expcast", 0.1)] * 2
+    # one sequence: the call's own result, no copy; dense forward the same
+    del calls[:]
+    one = adapter.forward_varlen(q, q, q, cu_seqlens=cu[[0, 2]], max_seqlen=258, cu_seqlens_host=(0, 258))
+    assert one.shape == q.shape and calls == [((258, 2, 128), "open-vc", "expcast", 0.1)]
+    assert adapter.forward(q, q, q).shape == q.shape
+    # trailing padding rows are zero and never attended
+    del calls[:]
+    padded = DenseDiffusionAdapter(2, 128, 0.1, packed_trailing_padding=True)
+    out = padded.forward_varlen(q, q, q, cu_seqlens=cu, max_seqlen=129, cu_seqlens_host=(0, 129, 258))
+    assert len(calls) == 1 and bool((out[:129] == 1).all()) and bool((out[129:] == 0).all())
+    # metadata faults
+    with pytest.raises(ValueError, match="matching"):
+        adapter.forward_varlen(q, q[:100], q, cu_seqlens=cu, max_seqlen=129, cu_seqlens_host=(0, 129, 258))
+    with pytest.raises(ValueError, match="same bounds"):
+        adapter.forward_varlen(q, q, q, cu_seqlens=cu.long(), max_seqlen=129, cu_seqlens_host=(0, 129, 258))
+    with pytest.raises(ValueError, match="same bounds"):
+        adapter.forward_varlen(q, q, q, cu_seqlens=cu[:2], max_seqlen=129, cu_seqlens_host=(0, 129, 258))
+    with pytest.raises(ValueError, match="cu_seqlens_host is required"):
+        adapter.forward_varlen(q, q, q, cu_seqlens=cu, max_seqlen=129)
+
+
+def test_sglang_registration_needs_sglang():
+    try:
+        import sglang  # noqa: F401
+    except ImportError:
+        with pytest.raises(ImportError, match="sglang"):
+            import open_vc_attn.integrations.sglang  # noqa: F401
+    else:
+        from open_vc_attn.integrations import DenseDiffusionAdapter
+        from open_vc_attn.integrations.sglang import OpenVCAttentionBackend
+
+        assert OpenVCAttentionBackend.get_supported_head_sizes() == [128]
+        assert issubclass(OpenVCAttentionBackend.get_impl_cls(), DenseDiffusionAdapter)
+
+
+REFERENCE_PACKED = "/root/reference/src/open_vc_attn/integrations/packed.py"
+
+
+@pytest.mark.skipif(not os.path.isfile(REFERENCE_PACKED), reason="needs a checkout of the reference beside this repository")
+def test_packed_bounds_agree_with_the_reference_on_random_metadata():
+    """The reference's own segments(), read where it lies, against this package's on 3000 random cases (valid and
+    faulty): same pieces or a ValueError with the same text."""
+    import importlib.util
+    import random
+
+    from open_vc_attn.integrations import segments
+
+    spec = importlib.util.spec_from_file_location("reference_packed", REFERENCE_PACKED)
+    theirs = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(theirs)
+    rng = random.Random(7)
+    for _ in range(3000):
+        count = rng.randint(1, 4)
+        edges = sorted(rng.sample(range(1, 40), count))
+        bounds = [0] + edges
+        mutation = rng.randint(0, 9)
+        if mutation == 0:
+            bounds[0] = 1
+        elif mutation == 1:
+            bounds[rng.randrange(len(bounds))] = float(bounds[-1])
+        elif mutation == 2 and len(bounds) > 2:
+            bounds[1] = bounds[2]
+        elif mutation == 3:
+            bounds = None
+        total = edges[-1] + (1 if mutation == 4 else 0)
+        longest = rng.choice([0, 1, 5, 20, 40] + edges)
+        padding = rng.random() < 0.5
+
+        def run(fn):
+            try:
+                return [tuple(piece) for piece in fn(None if bounds is None else tuple(bounds), total, longest, trailing_padding=padding)]
+            except ValueError as error:
+                return str(error)
+
+        assert run(segments) == run(theirs.segments), (bounds, total, longest, padding)
 
 
 def test_benchmark_statistics_and_shapes():
