@@ -266,7 +266,11 @@ def test_sglang_registration_needs_sglang():
         assert issubclass(OpenVCAttentionBackend.get_impl_cls(), DenseDiffusionAdapter)
 
 
-REFERENCE_PACKED = "/root/reference/src/open_vc_attn/integrations/packed.py"
+# a checkout of the reference beside this repository (or wherever REFERENCE_SRC points)
+REFERENCE_PACKED = os.path.join(
+    os.environ.get("REFERENCE_SRC") or os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))), "reference", "src"),
+    "open_vc_attn", "integrations", "packed.py",
+)
 
 
 @pytest.mark.skipif(not os.path.isfile(REFERENCE_PACKED), reason="needs a checkout of the reference beside this repository")
