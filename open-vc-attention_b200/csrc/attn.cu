@@ -1083,7 +1083,8 @@ extern "C" int ovc_attention_vsmooth(const void* q8, const void* k8, const void*
                                      const float* means, const float* channel_scale, void* workspace, void* out,
                                      int64_t Sq, int64_t Sk, int64_t H, float softmax_scale, int mid_window_blocks,
                                      uint32_t* status, void* stream) {
-    if (!means || !channel_scale || !unit_descale || !aligned16(means) || !aligned16(channel_scale)) return OVC_ERR_ARGUMENT;
+    if (!means || !channel_scale || !unit_descale || !aligned16(means) || !aligned16(channel_scale) || H > 65535)
+        return OVC_ERR_ARGUMENT;  // (the means are split by a grid with one row of CTAs per head)
     const int64_t blocks = ceil_div(Sq > Sk ? Sq : Sk, kTile);
     // unit_descale: at least H * ceil(max(Sq,Sk)/128) floats equal to 1.0 (no Q/K/V descales on this path).
     return launch_attention(q8, k8, v_packed, unit_descale, blocks, unit_descale, unit_descale, nullptr, 0, means,
