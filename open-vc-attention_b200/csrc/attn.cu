@@ -383,17 +383,6 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
                 for (int it = 0; it < n_iters; ++it) {
                     const int j = tile_at(it, j0, p.first_tile, n_tiles);
                     const int ks = it % kKStages, vs = it % kVStages;
-                    if (kVS && (it == 0 || j / kMeanGroup != j_before / kMeanGroup)) {
-                        // The scan enters another group of 32 key blocks: fetch its means.  The buffer's previous
-                        // group was left two groups ago; the PV issuer commits m_free when it leaves a group.
-                        const int b = issued_m & 1;
-                        if (issued_m >= 2 && !wait_bar(sm, &sm.m_free[b], ((issued_m >> 1) - 1) & 1, p.status)) break;
-                        mbar_expect_tx(smem_addr(&sm.m_full[b]), kTileBytes);
-                        if constexpr (kVS)
-                            tma_load_4d(smem_addr(sm.means[b]), &means_map.map, smem_addr(&sm.m_full[b]), (j / kMeanGroup) * 128, 0, head, 0, keep);
-                        ++issued_m;
-                    }
-                    j_before = j;
                     // K(it - kKStages) was last read by stage 1's QK of that step; stage 1 releases the slot
                     // when it sees those scores.
                     if (it >= kKStages &&
@@ -410,6 +399,20 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
                     mbar_expect_tx(smem_addr(&sm.v_full[vs]), kTileBytes);
                     tma_load_4d(smem_addr(sm.v[vs]), &tmap_v, smem_addr(&sm.v_full[vs]), j * kTile, 0, head, batch, keep);
                     issued_v = it + 1;
+                    if (kVS && (it == 0 || j / kMeanGroup != j_before / kMeanGroup)) {
+                        // The scan enters another group of 32 key blocks: fetch its means.  The buffer's previous
+                        // group was left two groups ago; the PV issuer commits m_free when it leaves a group, at
+                        // the step that enters the group before this one.  That step needs K of its successor
+                        // (the relay hands "K(n+1) landed" over before "V(n) landed"), which may be this very
+                        // iteration's tile: so the wait comes after this iteration's K and V loads, never before.
+                        const int b = issued_m & 1;
+                        if (issued_m >= 2 && !wait_bar(sm, &sm.m_free[b], ((issued_m >> 1) - 1) & 1, p.status)) break;
+                        mbar_expect_tx(smem_addr(&sm.m_full[b]), kTileBytes);
+                        if constexpr (kVS)
+                            tma_load_4d(smem_addr(sm.means[b]), &means_map.map, smem_addr(&sm.m_full[b]), (j / kMeanGroup) * 128, 0, head, 0, keep);
+                        ++issued_m;
+                    }
+                    j_before = j;
                 }
                 if (kVS) {
                     // A group whose blocks never complete a slice has no reader: its copy must still have landed

@@ -190,6 +190,47 @@ def test_long_scans_restore_means_on_the_tensor_core(s, h, window, exact_bf16_me
     assert error < ORACLE_TOL
 
 
+@pytest.mark.parametrize("blocks", [17, 32, 33, 34, 49, 64, 65, 66, 97, 129])
+def test_every_scan_order_completes(blocks):
+    """The means tiles (32 key blocks each) are loaded, read and released through barriers of their own; which
+    group follows which depends on the length and on the window (a group of a single block at the turn of the
+    mid-window order once made the loader wait for a step that needed the loader).  Every combination must finish
+    without an expired wait, and the cases that used to stall must match the oracle."""
+    _, baselines, forward, _ = _modules()
+    from open_vc_attn.api import raw_forward
+
+    s = 128 * (blocks - 1) + 113
+    q, k, v = structured_qkv(s, 1, seed=blocks)
+    prepared = baselines.prepare_vc(q, k, v, clusters=16, iterations=1)
+    for window in (None, 0, 1, 4, 17, 40):
+        out, _ = raw_forward(prepared.q, prepared.k, prepared.v, expcast=True, mid_window_blocks=window,
+                             **prepared.forward_kwargs())
+        forward.check_status(q.device)
+        assert torch.isfinite(out).all(), (blocks, window)
+
+
+@pytest.mark.parametrize("s,h,window", [(4209, 2, 4), (12379, 1, 17)])
+def test_single_block_group_at_the_turn_of_the_scan(s, h, window):
+    _, baselines, forward, _ = _modules()
+    from open_vc_attn.api import raw_forward
+
+    q, k, v = structured_qkv(s, h, seed=s)
+    prepared = baselines.prepare_vc(q, k, v, clusters=32, iterations=1)
+    out, _ = raw_forward(prepared.q, prepared.k, prepared.v, expcast=True, mid_window_blocks=window,
+                         **prepared.forward_kwargs())
+    forward.check_status(q.device)
+    blocks = (s + 127) // 128
+    m_blocks = [0, 3, (blocks - 1) // 2]
+    ones = np.ones((h, blocks), dtype=np.float32)
+    want = oatt.expcast_attention(
+        u8(prepared.q), u8(prepared.k), u8(prepared.v), ones, ones, np.ones(h, dtype=np.float32), mid_window_blocks=window,
+        rows=m_blocks, v_smooth_means=f32(prepared.means).reshape(blocks, h, 128),
+        v_channel_scale=f32(prepared.scale).reshape(h, 128),
+    )
+    rows = np.concatenate([np.arange(256 * m, min(256 * m + 256, s)) for m in m_blocks])
+    assert oatt.relative_l2(f32(out)[rows], want[rows]) < ORACLE_TOL
+
+
 def test_reuse_path_is_graph_capturable():
     # tests/gpu/test_attention.py:128-150 of the reference
     _, baselines, _, _ = _modules()
