@@ -3,7 +3,8 @@
 Heads are independent on this path (Q/K are quantised per 128 tokens per head, V per head), so a caller
 whose tensors live in pinned host memory does not have to wait for all of Q, K, V to arrive before the
 first kernel starts: ``attention_host`` copies group g+1 in while group g is computed and group g-1 is
-copied out, on three streams with two device buffers per tensor.  The result equals
+copied out, on a copy-in, a copy-out and two compute streams with two device buffers per tensor (the kernels
+of consecutive groups overlap at their ragged last waves; the first group is one head).  The result equals
 ``attention(q.cuda(), k.cuda(), v.cuda())`` bit for bit.  The reference has no such helper (its callers keep
 tensors on the device); the copies are ``ovc_copy_head_slice`` of libovc.so.
 """
@@ -33,7 +34,10 @@ class HostAttention:
         self.device = torch.device(device)
         self.group = min(heads_per_group, heads)
         with torch.cuda.device(self.device):
-            self.copy_in, self.compute, self.copy_out = (torch.cuda.Stream() for _ in range(3))
+            self.copy_in, self.copy_out = torch.cuda.Stream(), torch.cuda.Stream()
+            # One compute stream per buffer slot: the kernels of consecutive groups may overlap, so that the next
+            # group's CTAs fill the SMs that the previous group's last, partial wave leaves idle.
+            self.compute = [torch.cuda.Stream(), torch.cuda.Stream()]
             shape = (length, self.group, 128)
             self.inputs = [[torch.empty(shape, dtype=dtype, device=self.device) for _ in range(3)] for _ in range(2)]
             self.landed = [torch.cuda.Event() for _ in range(2)]
@@ -53,34 +57,39 @@ class HostAttention:
             raise ValueError("out must be a contiguous pinned bfloat16 host tensor of Q's shape")
         lib = _lib.load()
         caller = torch.cuda.current_stream(self.device)
-        starts = list(range(0, self.heads, self.group))
+        # Head groups in order.  The first group is a single head, so that the first kernel starts after one
+        # head's copies instead of a whole group's (nothing overlaps that first copy); a remainder comes last.
+        lead = 1 if self.group > 1 and self.heads > self.group else 0
+        starts = ([0] if lead else []) + list(range(lead, self.heads, self.group))
         with torch.cuda.device(self.device):
-            for stream in (self.copy_in, self.compute, self.copy_out):
+            for stream in (self.copy_in, self.copy_out, *self.compute):
                 stream.wait_stream(caller)
             for index, first in enumerate(starts):
                 slot = index & 1
-                count = min(self.group, self.heads - first)
+                count = 1 if (lead and index == 0) else min(self.group, self.heads - first)
                 if index >= 2:
                     self.copy_in.wait_event(self.consumed[slot])  # the group that used this buffer has been computed
                 for buffer, source in zip(self.inputs[slot], (q, k, v)):
                     # a last, smaller group goes into the leading heads of the buffer
                     _copy(lib, buffer, 0, source, first, count, True, self.copy_in)
                 self.landed[slot].record(self.copy_in)
-                self.compute.wait_event(self.landed[slot])
+                compute = self.compute[slot]
+                compute.wait_event(self.landed[slot])
                 if index >= 2:
-                    self.compute.wait_event(self.stored[slot])  # the result that lived in this slot has left
-                with torch.cuda.stream(self.compute):
+                    compute.wait_event(self.stored[slot])  # the result that lived in this slot has left
+                with torch.cuda.stream(compute):
                     if count == self.group:
                         args = self.inputs[slot]
                     else:
                         args = [buffer[:, :count].contiguous() for buffer in self.inputs[slot]]
                     self.results[slot] = api.attention(*args, **attention_options)
-                self.consumed[slot].record(self.compute)
+                self.consumed[slot].record(compute)
                 self.copy_out.wait_event(self.consumed[slot])
                 _copy(lib, out, first, self.results[slot], 0, count, False, self.copy_out)
                 self.stored[slot].record(self.copy_out)
             caller.wait_stream(self.copy_out)
-            caller.wait_stream(self.compute)
+            for compute in self.compute:
+                caller.wait_stream(compute)
             caller.wait_stream(self.copy_in)
         return out
 

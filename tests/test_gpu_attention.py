@@ -298,7 +298,7 @@ def test_causal_mask(sq, sk, h):
                         v_descale=prepared.v_descale, expcast=True, causal=True, mid_window_blocks=4)
 
 
-@pytest.mark.parametrize("s,h,group", [(700, 5, 2), (1024, 8, 8), (2000, 3, 4)])
+@pytest.mark.parametrize("s,h,group", [(700, 5, 2), (1024, 8, 8), (2000, 3, 4), (900, 7, 3), (600, 6, 4)])
 def test_host_streaming_equals_the_device_call(s, h, group):
     """attention_host: head groups streamed from pinned host memory give the device result bit for bit."""
     ovc, api, forward = _api()
