@@ -227,21 +227,19 @@ __device__ __forceinline__ void encode128(const uint32_t (&s)[128], uint64_t sca
     }
 }
 
-// Row max of 128 scores: three-input max tree (64 instructions).
+// Row max of 128 scores: a three-input max tree per 32 columns (the order in which a tensor-memory load fills
+// the registers), then the four partial results; 64 instructions.
+__device__ __forceinline__ float max32(const uint32_t* s) {
+    float a[11];
+#pragma unroll
+    for (int c = 0; c < 10; ++c)
+        a[c] = fmax3(__uint_as_float(s[3 * c]), __uint_as_float(s[3 * c + 1]), __uint_as_float(s[3 * c + 2]));
+    a[10] = fmaxf(__uint_as_float(s[30]), __uint_as_float(s[31]));
+    const float b0 = fmax3(a[0], a[1], a[2]), b1 = fmax3(a[3], a[4], a[5]), b2 = fmax3(a[6], a[7], a[8]);
+    return fmax3(fmax3(b0, b1, b2), a[9], a[10]);
+}
 __device__ __forceinline__ float max128(const uint32_t (&s)[128]) {
-    float m9[43];
-#pragma unroll
-    for (int c = 0; c < 42; ++c)
-        m9[c] = fmax3(__uint_as_float(s[3 * c]), __uint_as_float(s[3 * c + 1]), __uint_as_float(s[3 * c + 2]));
-    m9[42] = fmaxf(__uint_as_float(s[126]), __uint_as_float(s[127]));
-    float m3[15];
-#pragma unroll
-    for (int c = 0; c < 14; ++c) m3[c] = fmax3(m9[3 * c], m9[3 * c + 1], m9[3 * c + 2]);
-    m3[14] = m9[42];
-    float m1[5];
-#pragma unroll
-    for (int c = 0; c < 5; ++c) m1[c] = fmax3(m3[3 * c], m3[3 * c + 1], m3[3 * c + 2]);
-    return fmaxf(fmax3(m1[0], m1[1], m1[2]), fmaxf(m1[3], m1[4]));
+    return fmaxf(fmax3(max32(s), max32(s + 32), max32(s + 64)), max32(s + 96));
 }
 
 __device__ __forceinline__ uint32_t bf16x2(float lo, float hi) {
