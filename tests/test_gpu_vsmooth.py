@@ -231,6 +231,31 @@ def test_single_block_group_at_the_turn_of_the_scan(s, h, window):
     assert oatt.relative_l2(f32(out)[rows], want[rows]) < ORACLE_TOL
 
 
+def test_headline_length_against_the_oracle():
+    """S = 73397 (574 key blocks, 18 tiles of means through the two buffers), both scan orders, sampled query blocks."""
+    _, baselines, forward, _ = _modules()
+    from open_vc_attn.api import raw_forward
+
+    s, h = 73397, 2
+    q, k, v = structured_qkv(s, h, seed=99)
+    prepared = baselines.prepare_vc(q, k, v, clusters=64, iterations=1)
+    blocks = (s + 127) // 128
+    ones = np.ones((h, blocks), dtype=np.float32)
+    for window, m_blocks in ((None, [0, 286]), (4, [143])):
+        out, _ = raw_forward(prepared.q, prepared.k, prepared.v, expcast=True, mid_window_blocks=window,
+                             **prepared.forward_kwargs())
+        forward.check_status(q.device)
+        want = oatt.expcast_attention(
+            u8(prepared.q), u8(prepared.k), u8(prepared.v), ones, ones, np.ones(h, dtype=np.float32),
+            mid_window_blocks=window, rows=m_blocks, v_smooth_means=f32(prepared.means).reshape(blocks, h, 128),
+            v_channel_scale=f32(prepared.scale).reshape(h, 128),
+        )
+        rows = np.concatenate([np.arange(256 * m, min(256 * m + 256, s)) for m in m_blocks])
+        error = oatt.relative_l2(f32(out)[rows], want[rows])
+        print(f"window={window}: rel-L2 vs oracle {error:.2e}")
+        assert error < ORACLE_TOL
+
+
 def test_reuse_path_is_graph_capturable():
     # tests/gpu/test_attention.py:128-150 of the reference
     _, baselines, _, _ = _modules()
