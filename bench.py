@@ -41,7 +41,7 @@ CONFIGS = {
     "c3": dict(B=1, S=73397, H=56, dtype="bf16", values="video-DiT-like (4 outlier channels x8, LogNormal(0,0.3) token norms, V ~ N(mu_h,1))",
                call="attention", launches=4),
     "c2": dict(B=1, S=32768, H=8, dtype="bf16", values="i.i.d. N(0,1)", call="attention", launches=4),
-    "c4": dict(B=4, S=8191, H=24, dtype="fp16", values="i.i.d. N(0,1)", call="attention", launches=6),
+    "c4": dict(B=4, S=8191, H=24, dtype="fp16", values="i.i.d. N(0,1)", call="attention", launches=5),
     "c5": dict(B=1, S=73397, H=14, dtype="bf16", values="Q,K i.i.d. N(0,1), V Student-t(3)", call="v_repair budget 0.005",
                launches=7),
 }

@@ -41,6 +41,10 @@ extern "C" {
 #define OVC_ERR_TOO_LARGE (-5)   /* a size exceeds what the library's built-in scratch memory can hold */
 
 /* Bits of the device status word written by ovc_attention (0 = clean run). */
+/* flags of ovc_attention_ex */
+#define OVC_ATTN_CAUSAL 1     /* bottom-right aligned causal mask */
+#define OVC_ATTN_V_UNPACKED 2 /* v is [B,Sk,H,128] FP8 (the layout of the quantisers' output), not the packed one */
+
 #define OVC_STATUS_WAIT_EXPIRED 1u /* a bounded barrier wait gave up; the output rows of that launch hold NaN */
 
 int ovc_version(void);
@@ -213,12 +217,16 @@ int ovc_copy_head_slice(void* dst, int64_t dst_heads, int64_t dst_first, const v
  *           (m * sigma + log2(l) - 8) * ln 2 with m the row maximum of the descaled scores,
  *           sigma = softmax_scale * log2(e) * q_descale and l the denominator; -inf for a row whose l is 0 or NaN
  *           (cute/flash_fwd_sm100.py:4437-4475).
- *   causal  non-zero: key column c is visible to query row r iff c < r + 1 + Sk - Sq (cute/mask.py:186-199);
- *           tiles wholly above the diagonal are skipped.  Needs mid_window_blocks = -1 and no repair prefix.
+ *   flags   OVC_ATTN_CAUSAL: key column c is visible to query row r iff c < r + 1 + Sk - Sq
+ *           (cute/mask.py:186-199); tiles wholly above the diagonal are skipped.  Needs mid_window_blocks = -1 and
+ *           no repair prefix.
+ *           OVC_ATTN_V_UNPACKED: `v_packed` points to V codes in the [B,Sk,H,128] layout instead, which the
+ *           kernel reads as the MN-major operand of P V (cute/flash_fwd_sm100.py:726-729,767-770: the reference's
+ *           general path does the same), so no packing pass is needed; not with a repair prefix.
  */
 int ovc_attention_ex(const void* q8, const void* k8, const void* v_packed, const float* q_descale,
                      int64_t q_blocks, const float* k_descale, const float* v_descale, const float* repair_kd,
-                     int64_t repair_rows, void* out, float* lse, int causal, int64_t B, int64_t Sq, int64_t Sk,
+                     int64_t repair_rows, void* out, float* lse, int flags, int64_t B, int64_t Sq, int64_t Sk,
                      int64_t H, float softmax_scale, int mid_window_blocks, uint32_t* status, void* stream);
 
 /* ---- VC-Attention baseline: V-Smooth preparation and the mean-restoring attention variant ----

@@ -58,7 +58,7 @@ constexpr uint32_t kColS = 0, kColP = 128, kColO = 192, kColW = 480, kTmemCols =
 constexpr long long kWaitCycles = 400000000LL;    // bounded barrier wait (~0.2 s)
 constexpr uint32_t kSleepHintNs = 100000;         // one hardware-suspended try_wait lasts at most this
 
-template <bool kVS>
+template <bool kVS, bool kVNat>
 struct SmemLayout {
     alignas(1024) uint8_t q[2][kTileBytes];
     alignas(1024) uint8_t k[kKStages][kTileBytes];
@@ -77,6 +77,9 @@ struct SmemLayout {
     // V-Smooth only (a stub in the other variants): two tiles of block means, 128 channels x 128 bytes = BF16 high
     // parts of 32 key blocks, then their low parts, in the 128-byte swizzle.
     alignas(1024) uint8_t means[kVS ? 2 : 1][kVS ? kTileBytes : 16];
+    // V in its [S,H,128] layout only (a stub otherwise): 128 rows of E4M3 1.0, the continuation of every V tile
+    // along N (the MN-major operand's next 128-byte column), which makes the PV product sum P.
+    alignas(1024) uint8_t ones[kVNat ? kTileBytes : 16];
 };
 
 struct AttnParams {
@@ -282,13 +285,13 @@ struct MeansMap<false> {
     int unused;
 };
 
-template <bool kVS, bool kCausal, bool kRepair>
+template <bool kVS, bool kCausal, bool kRepair, bool kVNat>
 __global__ void __launch_bounds__(kThreads, 1)
 attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                  const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ MeansMap<kVS> means_map,
                  const AttnParams p) {
     extern __shared__ uint8_t smem_raw[];
-    using Layout = SmemLayout<kVS>;
+    using Layout = SmemLayout<kVS, kVNat>;
     Layout& sm = *reinterpret_cast<Layout*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -353,6 +356,9 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         const int slot = i / (ext_rows(kVS) * 128 / 4), w = i % (ext_rows(kVS) * 128 / 4);
         reinterpret_cast<uint32_t*>(&sm.v[slot][kTileBytes])[w] = kVS ? 0u : 0x38383838u;
     }
+    if (kVNat) {
+        for (int i = threadIdx.x; i < kTileBytes / 4; i += kThreads) reinterpret_cast<uint32_t*>(sm.ones)[i] = 0x38383838u;
+    }
     fence_proxy_async_smem();
     if (warp == 9) {
         tmem_alloc(smem_addr(&sm.tmem_base), kTmemCols);
@@ -395,7 +401,10 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
                         !wait_bar(sm, &sm.v_empty[vs], (it / kVStages - 1) & 1, p.status))
                         break;
                     mbar_expect_tx(smem_addr(&sm.v_full[vs]), kTileBytes);
-                    tma_load_4d(smem_addr(sm.v[vs]), &tmap_v, smem_addr(&sm.v_full[vs]), j * kTile, 0, head, batch, keep);
+                    if (kVNat)  // [keys, head, 128 channels] like a K tile
+                        tma_load_4d(smem_addr(sm.v[vs]), &tmap_v, smem_addr(&sm.v_full[vs]), 0, head, j * kTile, batch, keep);
+                    else
+                        tma_load_4d(smem_addr(sm.v[vs]), &tmap_v, smem_addr(&sm.v_full[vs]), j * kTile, 0, head, batch, keep);
                     issued_v = it + 1;
                     if (kVS && (it == 0 || j / kMeanGroup != j_before / kMeanGroup)) {
                         // The scan enters another group of 32 key blocks: fetch its means.  The buffer's previous
@@ -471,8 +480,9 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         } else if (warp == 11) {
             // ---------------- PV issuer ----------------
             // p_full[s] completion n: stage s has stored P_s(n) and V(n) has landed.
-            constexpr uint32_t idesc_pv = idesc_e4m3_f32(pv_n(kVS));
-            constexpr uint32_t kColOStride = pv_n(kVS);
+            // (The MN-major operand comes in units of 16 columns: N = 144, all sixteen extra columns sum P.)
+            constexpr uint32_t idesc_pv = kVNat ? idesc_e4m3_f32_bmn(pv_n(true)) : idesc_e4m3_f32(pv_n(kVS));
+            constexpr uint32_t kColOStride = pv_n(kVS || kVNat);
             constexpr uint32_t idesc_mean = idesc_bf16_f32(kDim);
             bool ok = true;
             int groups_left = 0;  // V-Smooth: groups of block means the scan has left (buffer groups_left & 1 is current)
@@ -501,8 +511,14 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
                         mma_bf16_ts(tmem + kColO + s * kColOStride, w_lo, mean_lo, idesc_mean);
                         mma_bf16_ts(tmem + kColO + s * kColOStride, w_hi, mean_lo + 4, idesc_mean);
                     }
-                    mma4_f8_ts(tmem + kColO + s * kColOStride, tmem + kColP + 32 * s,
-                               smem_desc_lo(smem_addr(sm.v[n % kVStages])), idesc_pv, n > 0 ? 1u : 0u);
+                    if (kVNat) {
+                        const uint32_t slot = smem_addr(sm.v[n % kVStages]);
+                        mma4_f8_ts_bmn(tmem + kColO + s * kColOStride, tmem + kColP + 32 * s,
+                                       smem_desc_lo_bmn(slot, smem_addr(sm.ones) - slot), idesc_pv, n > 0 ? 1u : 0u);
+                    } else {
+                        mma4_f8_ts(tmem + kColO + s * kColOStride, tmem + kColP + 32 * s,
+                                   smem_desc_lo(smem_addr(sm.v[n % kVStages])), idesc_pv, n > 0 ? 1u : 0u);
+                    }
                     if (kVS && leave_group && s == 1) mma_commit_elect(smem_addr(&sm.m_free[groups_left & 1]));
                     mma_commit_elect(smem_addr(n + 1 < n_iters ? &sm.pv_done[s] : &sm.o_full[s]));
                 }
@@ -549,7 +565,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         const int row_in_tile = (warp & 3) * 32 + lane;
         const uint32_t lane_base = tmem + (static_cast<uint32_t>((warp & 3) * 32) << 16);
         const uint32_t t_s = lane_base + kColS, t_p = lane_base + kColP + 32 * stage;
-        const uint32_t t_o = lane_base + kColO + stage * pv_n(kVS);
+        const uint32_t t_o = lane_base + kColO + stage * pv_n(kVS || kVNat);
         const int q_tile = 2 * m_block + stage;
         const long long bh_l = static_cast<long long>(batch) * p.H + head;
         const float qd = q_tile < p.q_blocks ? __ldg(p.q_descale + bh_l * p.q_blocks + q_tile) : 1.0f;
@@ -950,10 +966,13 @@ namespace {
 
 int launch_attention(const void* q8, const void* k8, const void* v_packed, const float* q_descale, int64_t q_blocks,
                      const float* k_descale, const float* v_descale, const float* repair_kd, int64_t repair_rows,
-                     const float* vs_means, const float* vs_scale, void* vs_workspace, void* out, float* lse, int causal, int64_t B,
+                     const float* vs_means, const float* vs_scale, void* vs_workspace, void* out, float* lse, int flags, int64_t B,
                      int64_t Sq, int64_t Sk, int64_t H, float softmax_scale, int mid_window_blocks, uint32_t* status,
                      void* stream) {
+    if ((flags & ~(OVC_ATTN_CAUSAL | OVC_ATTN_V_UNPACKED)) != 0) return OVC_ERR_ARGUMENT;
+    const bool causal = (flags & OVC_ATTN_CAUSAL) != 0, v_natural = (flags & OVC_ATTN_V_UNPACKED) != 0;
     if (causal && (mid_window_blocks != -1 || repair_rows != 0 || vs_means != nullptr)) return OVC_ERR_ARGUMENT;
+    if (v_natural && (repair_rows != 0 || vs_means != nullptr)) return OVC_ERR_ARGUMENT;
     if (!q8 || !k8 || !v_packed || !q_descale || !k_descale || !v_descale || !out || B < 1 || Sq < 1 || Sk < 1 ||
         H < 1 || Sq > (1LL << 30) || Sk > (1LL << 30) || q_blocks < ceil_div(Sq, kTile) || !(softmax_scale > 0.0f) ||
         !isfinite(softmax_scale) || mid_window_blocks < -1 || repair_rows < 0 || repair_rows % kTile != 0 ||
@@ -988,7 +1007,8 @@ int launch_attention(const void* q8, const void* k8, const void* v_packed, const
         const cuuint64_t dv[4] = {static_cast<cuuint64_t>(Sk), 128, static_cast<cuuint64_t>(H), static_cast<cuuint64_t>(B)};
         const cuuint64_t sv[3] = {static_cast<cuuint64_t>(Sk_pad), static_cast<cuuint64_t>(Sk_pad) * 128,
                                   static_cast<cuuint64_t>(Sk_pad) * 128 * H};
-        rc = make_map(&map_v, v_packed, dv, sv, 128, 128, 1);
+        // V in [B,Sk,H,128] is loaded like K: a box of 128 channels x 128 keys, keys past Sk read as zero.
+        rc = v_natural ? make_map(&map_v, v_packed, dk, sk, 128, 128, 2) : make_map(&map_v, v_packed, dv, sv, 128, 128, 1);
         if (rc != OVC_OK) return rc;
         if (vs_means != nullptr) {
             // Rows of n_groups x 128 bytes per (head, channel): see means_split_kernel.
@@ -1010,17 +1030,21 @@ int launch_attention(const void* q8, const void* k8, const void* v_packed, const
     p.mid_window = mid_window_blocks;
     p.scale_log2 = static_cast<float>(static_cast<double>(softmax_scale) * 1.4426950408889634);
 
-    const size_t smem_vs = sizeof(SmemLayout<true>) + 1024, smem_plain = sizeof(SmemLayout<false>) + 1024;
-    const size_t smem_bytes = vs_means != nullptr ? smem_vs : smem_plain;
+    const size_t smem_vs = sizeof(SmemLayout<true, false>) + 1024, smem_plain = sizeof(SmemLayout<false, false>) + 1024;
+    const size_t smem_nat = sizeof(SmemLayout<false, true>) + 1024;
+    const size_t smem_bytes = vs_means != nullptr ? smem_vs : (v_natural ? smem_nat : smem_plain);
     static std::atomic<bool> configured[64];
     if (device < 64 && !configured[device].load(std::memory_order_acquire)) {
-        err = cudaFuncSetAttribute(attention_kernel<false, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem_plain));
-        if (err == cudaSuccess)
-            err = cudaFuncSetAttribute(attention_kernel<false, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem_plain));
-        if (err == cudaSuccess)
-            err = cudaFuncSetAttribute(attention_kernel<true, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem_vs));
-        if (err == cudaSuccess)
-            err = cudaFuncSetAttribute(attention_kernel<false, true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem_plain));
+        const auto grow = [&err](const void* kernel, size_t bytes) {
+            if (err == cudaSuccess)
+                err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(bytes));
+        };
+        grow(reinterpret_cast<const void*>(attention_kernel<false, false, false, false>), smem_plain);
+        grow(reinterpret_cast<const void*>(attention_kernel<false, false, true, false>), smem_plain);
+        grow(reinterpret_cast<const void*>(attention_kernel<false, true, false, false>), smem_plain);
+        grow(reinterpret_cast<const void*>(attention_kernel<true, false, false, false>), smem_vs);
+        grow(reinterpret_cast<const void*>(attention_kernel<false, false, false, true>), smem_nat);
+        grow(reinterpret_cast<const void*>(attention_kernel<false, true, false, true>), smem_nat);
         if (err != cudaSuccess) { set_last_cuda_error(err); return OVC_ERR_CUDA; }
         configured[device].store(true, std::memory_order_release);
     }
@@ -1035,12 +1059,14 @@ int launch_attention(const void* q8, const void* k8, const void* v_packed, const
         const int n_groups = static_cast<int>(ceil_div(n_tiles, kMeanGroup));
         means_split_kernel<<<dim3(n_groups, static_cast<unsigned>(H)), kDim, 0, s>>>(
             vs_means, static_cast<uint4*>(vs_workspace), static_cast<int>(n_tiles), static_cast<int>(H), n_groups);
-        attention_kernel<true, false, false><<<grid, kThreads, smem_bytes, s>>>(map_q, map_k, map_v, map_m, p);
-    } else if (causal) {
-        attention_kernel<false, true, false><<<grid, kThreads, smem_bytes, s>>>(map_q, map_k, map_v, MeansMap<false>{}, p);
+        attention_kernel<true, false, false, false><<<grid, kThreads, smem_bytes, s>>>(map_q, map_k, map_v, map_m, p);
     } else {
-        if (repair_rows > 0) attention_kernel<false, false, true><<<grid, kThreads, smem_bytes, s>>>(map_q, map_k, map_v, MeansMap<false>{}, p);
-        else attention_kernel<false, false, false><<<grid, kThreads, smem_bytes, s>>>(map_q, map_k, map_v, MeansMap<false>{}, p);
+        const MeansMap<false> none{};
+        if (causal && v_natural) attention_kernel<false, true, false, true><<<grid, kThreads, smem_bytes, s>>>(map_q, map_k, map_v, none, p);
+        else if (causal) attention_kernel<false, true, false, false><<<grid, kThreads, smem_bytes, s>>>(map_q, map_k, map_v, none, p);
+        else if (v_natural) attention_kernel<false, false, false, true><<<grid, kThreads, smem_bytes, s>>>(map_q, map_k, map_v, none, p);
+        else if (repair_rows > 0) attention_kernel<false, false, true, false><<<grid, kThreads, smem_bytes, s>>>(map_q, map_k, map_v, none, p);
+        else attention_kernel<false, false, false, false><<<grid, kThreads, smem_bytes, s>>>(map_q, map_k, map_v, none, p);
     }
     return check_launch();
 }
@@ -1069,10 +1095,10 @@ extern "C" int ovc_attention(const void* q8, const void* k8, const void* v_packe
 
 extern "C" int ovc_attention_ex(const void* q8, const void* k8, const void* v_packed, const float* q_descale,
                                 int64_t q_blocks, const float* k_descale, const float* v_descale, const float* repair_kd,
-                                int64_t repair_rows, void* out, float* lse, int causal, int64_t B, int64_t Sq, int64_t Sk,
+                                int64_t repair_rows, void* out, float* lse, int flags, int64_t B, int64_t Sq, int64_t Sk,
                                 int64_t H, float softmax_scale, int mid_window_blocks, uint32_t* status, void* stream) {
     return launch_attention(q8, k8, v_packed, q_descale, q_blocks, k_descale, v_descale, repair_kd, repair_rows, nullptr,
-                            nullptr, nullptr, out, lse, causal, B, Sq, Sk, H, softmax_scale, mid_window_blocks, status, stream);
+                            nullptr, nullptr, out, lse, flags, B, Sq, Sk, H, softmax_scale, mid_window_blocks, status, stream);
 }
 
 extern "C" int64_t ovc_attention_vsmooth_workspace(int64_t Sk, int64_t H) {

@@ -193,6 +193,30 @@ __device__ __forceinline__ void mma4_f8_ts(uint32_t d_tmem, uint32_t a_tmem, uin
         : "r"(d_tmem), "r"(a_tmem), "r"(b_lo), "r"(kSmemDescHi), "r"(idesc), "r"(accumulate_first)
         : "memory");
 }
+// The same product with B in its MN-major form (rows of the shared-memory tile are the K index, 128 bytes of N per
+// row, 8-row groups 1024 bytes apart): a K-step of 32 rows advances the descriptor by 4 x 1024 bytes, and N beyond
+// the first 128 bytes continues `lbo` bytes after the tile (the leading-dimension offset in `b_lo`, bits 16-29).
+__device__ __forceinline__ void mma4_f8_ts_bmn(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo, uint32_t idesc,
+                                               uint32_t accumulate_first) {
+    asm volatile(
+        "{\n\t.reg .pred leader, p;\n\t.reg .b64 db;\n\t.reg .b32 bl, ta;\n\t"
+        "elect.sync _|leader, 0xFFFFFFFF;\n\t"
+        "setp.ne.b32 p, %5, 0;\n\t"
+        "mov.b64 db, {%2, %3};\n\t"
+        "@leader tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], [%1], db, %4, p;\n\t"
+        "add.u32 bl, %2, 256;\n\tadd.u32 ta, %1, 8;\n\tmov.b64 db, {bl, %3};\n\t"
+        "@leader tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], [ta], db, %4, 1;\n\t"
+        "add.u32 bl, %2, 512;\n\tadd.u32 ta, %1, 16;\n\tmov.b64 db, {bl, %3};\n\t"
+        "@leader tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], [ta], db, %4, 1;\n\t"
+        "add.u32 bl, %2, 768;\n\tadd.u32 ta, %1, 24;\n\tmov.b64 db, {bl, %3};\n\t"
+        "@leader tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], [ta], db, %4, 1;\n\t}"
+        :
+        : "r"(d_tmem), "r"(a_tmem), "r"(b_lo), "r"(kSmemDescHi), "r"(idesc), "r"(accumulate_first)
+        : "memory");
+}
+__device__ __forceinline__ uint32_t smem_desc_lo_bmn(uint32_t saddr, uint32_t lbo_bytes) {
+    return ((saddr & 0x3FFFFu) >> 4) | ((lbo_bytes >> 4) << 16);
+}
 // One BF16 x BF16 -> FP32 product of depth 16 added to the accumulator: A = 8 columns of tensor memory (two
 // BF16 values per column), B = 32 bytes of each 128-byte row of a swizzled shared-memory tile.
 __device__ __forceinline__ void mma_bf16_ts(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo, uint32_t idesc) {
@@ -222,6 +246,9 @@ __host__ __device__ constexpr uint32_t idesc_e4m3_f32(int n) {
            | (static_cast<uint32_t>(n >> 3) << 17)  // N / 8
            | (static_cast<uint32_t>(128 >> 4) << 24);  // M / 16
 }
+
+// The same with B MN-major (bit 16).
+__host__ __device__ constexpr uint32_t idesc_e4m3_f32_bmn(int n) { return idesc_e4m3_f32(n) | (1u << 16); }
 
 // Instruction descriptor for kind::f16, BF16 x BF16 -> F32, both operands K-major, M = 128.
 __host__ __device__ constexpr uint32_t idesc_bf16_f32(int n) {

@@ -11,6 +11,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 LIBRARY_PATH = os.path.join(os.path.dirname(_HERE), "lib", "libovc.so")
 
 OVC_F16, OVC_BF16 = 0, 1
+OVC_ATTN_CAUSAL, OVC_ATTN_V_UNPACKED = 1, 2  # flags of ovc_attention_ex
 STATUS_WAIT_EXPIRED = 1
 
 _p, _i, _l, _f = ctypes.c_void_p, ctypes.c_int, ctypes.c_int64, ctypes.c_float

@@ -210,9 +210,16 @@ def flash_attn_fwd(
     lib = _lib.load()
     _raise_if_flagged(device)
     with torch.cuda.device(device):
+        flags = _lib.OVC_ATTN_CAUSAL if causal else 0
         if v_prepacked:
             packed_ptr = v.data_ptr()
             keep = v
+        elif repair_rows == 0:
+            # V codes as the quantiser wrote them, [.., S, H, 128]: the kernel reads them as the MN-major operand
+            # of P V (what the reference's general path does, cute/flash_fwd_sm100.py:726-729), no packing pass.
+            keep = v.contiguous()
+            packed_ptr = keep.data_ptr()
+            flags |= _lib.OVC_ATTN_V_UNPACKED
         else:
             from .quantization import pack_v
 
@@ -223,14 +230,14 @@ def flash_attn_fwd(
         repair_ptr = None if repair_k_descale is None else repair_k_descale.data_ptr()
         tail = (batch, sq, sk, heads, float(softmax_scale), window, status_word(device).data_ptr(), _lib.stream_pointer(device))
         lse = None
-        if return_lse or causal:
+        if return_lse or flags:
             if return_lse:
                 lse = torch.empty((batch, heads, sq) if q.ndim == 4 else (heads, sq), dtype=torch.float32, device=device)
             _lib.check(
                 lib.ovc_attention_ex(
                     q.data_ptr(), k.data_ptr(), packed_ptr, q_descale.data_ptr(), q_descale.shape[2], k_descale.data_ptr(),
                     v_descale.data_ptr(), repair_ptr, repair_rows, out.data_ptr(), None if lse is None else lse.data_ptr(),
-                    1 if causal else 0, *tail,
+                    flags, *tail,
                 ),
                 "ovc_attention_ex",
             )

@@ -72,6 +72,8 @@ def test_null_and_bad_arguments_are_rejected_without_a_gpu(lib):
     assert lib.ovc_attention_ex(null, null, null, null, 1, null, null, null, 0, null, null, 0, 1, 128, 128, 1, 0.1, -1, null, null) == bad
     assert lib.ovc_attention_ex(p, p, p, p, 1, p, p, null, 0, p, null, 1, 1, 128, 128, 1, 0.1, 4, null, null) == bad   # causal + window
     assert lib.ovc_attention_ex(p, p, p, p, 1, p, p, p, 128, p, null, 1, 1, 128, 256, 1, 0.1, -1, null, null) == bad   # causal + repair
+    assert lib.ovc_attention_ex(p, p, p, p, 1, p, p, p, 128, p, null, 2, 1, 128, 256, 1, 0.1, -1, null, null) == bad   # unpacked V + repair
+    assert lib.ovc_attention_ex(p, p, p, p, 1, p, p, null, 0, p, null, 4, 1, 128, 128, 1, 0.1, -1, null, null) == bad   # unknown flag
     assert lib.ovc_attention_vsmooth(p, p, p, p, null, p, p, p, 128, 128, 1, 0.1, -1, null, null) == bad                # no means
     assert lib.ovc_attention_vsmooth(p, p, p, p, p + 4, p, p, p, 128, 128, 1, 0.1, -1, null, null) == bad               # misaligned means
     assert lib.ovc_attention_vsmooth(p, p, p, p, p, p, null, p, 128, 128, 1, 0.1, -1, null, null) == bad                # no workspace
