@@ -292,8 +292,8 @@ def main():
     keep("rcp_b", rcp_b)
     keep("rcp_r", hw_div(np.ones_like(rcp_b), rcp_b))
     rng = np.random.default_rng(7)
-    div_a = (rng.standard_normal(8192) * np.exp(4 * rng.standard_normal(8192))).astype(np.float32)
-    div_b = np.abs(rng.standard_normal(8192) * np.exp(4 * rng.standard_normal(8192))).astype(np.float32) + np.float32(1e-20)
+    div_a = (rng.standard_normal(65536) * np.exp(4 * rng.standard_normal(65536))).astype(np.float32)
+    div_b = np.abs(rng.standard_normal(65536) * np.exp(4 * rng.standard_normal(65536))).astype(np.float32) + np.float32(1e-20)
     div_q = hw_div(div_a, div_b)
     keep("div_a", div_a)
     keep("div_b", div_b)
